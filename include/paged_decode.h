@@ -1,0 +1,188 @@
+/*
+ * paged_decode.h — C ABI of the B200 (sm_100a) paged-KV grouped-query decode attention.
+ *
+ * The reference project is pure Python: its decode path is entered through
+ * pagedattn/triton_decode.py:285-377 (paged_decode_triton), which launches two Triton
+ * kernels.  It has no native interface to mirror, so this header defines the one a binding
+ * for that entry point needs: plain pointers, sizes and element strides, an int status on
+ * return, no exceptions, no torch types.  Every function is safe to call from several host
+ * threads; the library owns no device memory and keeps no mutable state keyed by shapes.
+ *
+ * Conventions
+ *   - all strides are in ELEMENTS of the tensor they describe, not bytes;
+ *   - head_dim is contiguous (stride 1) in q, out, k_cache and v_cache;
+ *   - k_cache and v_cache share strides (the reference uses K's strides for both,
+ *     pagedattn/triton_decode.py:329);
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream;
+ *   - return value 0 = success, negative = PD_ERR_*; nothing is launched on error.
+ */
+#ifndef PAGED_DECODE_B200_H_
+#define PAGED_DECODE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PD_ABI_VERSION 1
+
+/* status codes */
+#define PD_OK 0
+#define PD_ERR_INVALID_ARG (-1)   /* null pointer, bad size, bad stride, bad enum      */
+#define PD_ERR_UNSUPPORTED (-2)   /* valid request that no compiled kernel serves      */
+#define PD_ERR_WORKSPACE (-3)     /* workspace missing, misaligned or too small        */
+#define PD_ERR_CUDA (-4)          /* a CUDA runtime/driver call failed                 */
+
+/* kv_dtype: element type stored in k_cache / v_cache (pagedattn/config.py:16-31) */
+#define PD_KV_F16 0
+#define PD_KV_BF16 1
+#define PD_KV_E5M2 2
+#define PD_KV_I8 3
+
+/* io_dtype: element type of q and out */
+#define PD_IO_F16 0
+#define PD_IO_BF16 1
+
+/* kernel selector */
+#define PD_KERNEL_AUTO 0      /* streaming kernel when it serves the request, else the simple one */
+#define PD_KERNEL_SIMPLE 1    /* one CTA per (request, kv head, split); CUDA cores; any stride     */
+#define PD_KERNEL_STREAM 2    /* persistent TMA + mbarrier pipeline with tensor-core tiles         */
+
+/* bits of the optional device status word (PdDecodeArgs.status) */
+#define PD_DEV_BAD_BLOCK 1u   /* a block-table entry was outside [0, num_blocks): page skipped */
+#define PD_DEV_TIMEOUT 2u     /* a bounded wait inside a kernel gave up                        */
+
+/*
+ * Arguments of one decode step.  Replaces the argument list of paged_decode_triton
+ * (pagedattn/triton_decode.py:285-295) plus the fields of PagedKVCache it reads
+ * (pagedattn/cache.py:70-80).
+ */
+typedef struct PdDecodeArgs {
+  /* q [batch, num_q_heads, head_dim], out same shape; io_dtype elements */
+  const void* q;
+  void* out;
+  int64_t q_stride_b, q_stride_h;
+  int64_t out_stride_b, out_stride_h;
+
+  /* paged cache, NHD: [num_blocks, block_size, num_kv_heads, head_dim] */
+  const void* k_cache;
+  const void* v_cache;
+  int64_t kv_stride_block, kv_stride_token, kv_stride_head;
+
+  /* optional per-(token, head) fp16 scales [num_blocks, block_size, num_kv_heads], head
+   * stride 1 (pagedattn/triton_decode.py:145).  Required for PD_KV_I8, optional for
+   * PD_KV_E5M2 (an extension: the reference scales int8 only), must be NULL for 16-bit. */
+  const void* k_scale;
+  const void* v_scale;
+  int64_t scale_stride_block, scale_stride_token;
+
+  const int32_t* block_table; /* [batch, max_blocks_per_seq] physical block ids */
+  int64_t block_table_stride; /* row stride */
+  const int32_t* seq_lens;    /* [batch] tokens held per request; 0 gives a zero output row */
+
+  int32_t batch, num_q_heads, num_kv_heads, head_dim;
+  int32_t block_size, num_blocks, max_blocks_per_seq;
+  int32_t kv_dtype, io_dtype;
+
+  float sm_scale;     /* multiplies q.k before softmax; never re-derived from head_dim */
+  int32_t num_splits; /* >=1: cut every request's KV range into this many block_n-aligned
+                         chunks exactly as pagedattn/triton_decode.py:78-82 does;
+                         0: automatic (no host sync, seq_lens are never read on the host) */
+  int32_t block_n;    /* chunk alignment of the split rule, multiple of block_size; 0 = 64 */
+  int32_t kernel;     /* PD_KERNEL_* */
+  int32_t sm_count;   /* 0 = query the current device */
+  int32_t max_seq_len;/* upper bound on seq_lens if the caller knows one, else 0; only used
+                         to choose the automatic split count of PD_KERNEL_SIMPLE */
+
+  /* caller-owned scratch of at least pd_workspace_bytes() bytes, 256-byte aligned.
+   * Contents need not be initialised and are meaningless afterwards. */
+  void* workspace;
+  uint64_t workspace_bytes;
+
+  /* optional extra outputs for merging across devices: the softmax-normalised fp32 result
+   * [batch, num_q_heads, head_dim] (contiguous) and its base-2 log-sum-exp
+   * [batch, num_q_heads]; -inf marks an empty request.  Both or neither. */
+  float* result_f32;
+  float* result_lse;
+
+  uint32_t* status; /* optional device word, OR-ed with PD_DEV_* bits; caller zeroes it */
+  void* stream;
+} PdDecodeArgs;
+
+/* Host buffers for pd_decode_host. */
+typedef struct PdHostIO {
+  const void* q_host;             /* contiguous [batch, num_q_heads, head_dim] */
+  const int32_t* block_table_host;/* contiguous [batch, max_blocks_per_seq]    */
+  const int32_t* seq_lens_host;   /* [batch]                                   */
+  void* out_host;                 /* contiguous [batch, num_q_heads, head_dim] */
+} PdHostIO;
+
+/* Arguments of the stand-alone log-sum-exp merge.  Replaces _split_reduce_kernel's launch
+ * (pagedattn/triton_decode.py:198-240, 368-376) and also merges partial results that
+ * came from different GPUs. */
+typedef struct PdMergeArgs {
+  const float* part_out; /* normalised partial results, addressed [p][row][d] by strides */
+  const float* part_lse; /* base-2 log-sum-exp per (p, row); -inf = empty partial         */
+  int64_t out_stride_p, out_stride_row; /* d is contiguous                                */
+  int64_t lse_stride_p, lse_stride_row;
+  int32_t num_parts, num_rows, head_dim; /* rows = batch * num_q_heads */
+  void* out;                 /* [num_rows, head_dim] io_dtype, row stride below; may be NULL */
+  int64_t dst_stride_row;
+  int32_t io_dtype;
+  float* result_f32;         /* optional merged fp32 result [num_rows, head_dim] */
+  float* result_lse;         /* optional merged lse [num_rows]                   */
+  void* stream;
+} PdMergeArgs;
+
+/* Arguments of the debug gather: dense fp16 copy of the dequantised pages.  Replaces
+ * gather_contiguous (pagedattn/cache.py:187-215); uses the decode kernel's address
+ * function, so a bitwise comparison with a CPU gather checks the paging arithmetic. */
+typedef struct PdGatherArgs {
+  const PdDecodeArgs* cache; /* only the cache, scale, block-table and size fields are read */
+  void* k_dense;             /* [batch, num_kv_heads, s_max, head_dim] fp16, contiguous */
+  void* v_dense;
+  int32_t s_max;
+} PdGatherArgs;
+
+/* ABI version of the loaded library (PD_ABI_VERSION it was built with). */
+int pd_abi_version(void);
+
+/* Text for a status code; never NULL. */
+const char* pd_status_string(int status);
+
+/* One decode step on the device: out = softmax(sm_scale * q K^T) V per query head, over the
+ * pages the block table names.  Replaces paged_decode_triton
+ * (pagedattn/triton_decode.py:285-377). */
+int pd_decode(const PdDecodeArgs* args);
+
+/* The same step for callers that hold q, block_table, seq_lens and out in HOST memory:
+ * copies the three inputs into the device buffers named by `args` (which must be large
+ * enough), runs pd_decode, copies `out` back and waits for the stream.  The KV pages stay
+ * where they live, on the device.  No counterpart in the reference, whose callers pass
+ * CUDA tensors. */
+int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
+
+/* Bytes of workspace pd_decode needs for these arguments (depends on sizes, dtype, kernel
+ * and split count, not on data).  Replaces the reference's shape-keyed global scratch
+ * (_Workspace, pagedattn/triton_decode.py:266-282) with caller-owned memory. */
+int pd_workspace_bytes(const PdDecodeArgs* args, uint64_t* bytes);
+
+/* Which kernel pd_decode would run: PD_KERNEL_SIMPLE or PD_KERNEL_STREAM, or a negative
+ * PD_ERR_* if the arguments are rejected.  Touches no device. */
+int pd_select_kernel(const PdDecodeArgs* args);
+
+/* Split count heuristic for PD_KERNEL_SIMPLE.  Same signature and role as pick_num_splits
+ * (pagedattn/triton_decode.py:248-263); the policy is sized for B200's 148 SMs. */
+int pd_pick_num_splits(int batch, int num_kv_heads, int max_seq_len, int sm_count, int block_n);
+
+/* Log-sum-exp merge of partial results (see PdMergeArgs). */
+int pd_merge(const PdMergeArgs* args);
+
+/* Dense dequantised fp16 gather (see PdGatherArgs). */
+int pd_gather(const PdGatherArgs* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAGED_DECODE_B200_H_ */
