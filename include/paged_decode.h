@@ -27,6 +27,12 @@ extern "C" {
 
 #define PD_ABI_VERSION 1
 
+#if defined(__GNUC__)
+#define PD_API __attribute__((visibility("default")))
+#else
+#define PD_API
+#endif
+
 /* status codes */
 #define PD_OK 0
 #define PD_ERR_INVALID_ARG (-1)   /* null pointer, bad size, bad stride, bad enum      */
@@ -146,41 +152,41 @@ typedef struct PdGatherArgs {
 } PdGatherArgs;
 
 /* ABI version of the loaded library (PD_ABI_VERSION it was built with). */
-int pd_abi_version(void);
+PD_API int pd_abi_version(void);
 
 /* Text for a status code; never NULL. */
-const char* pd_status_string(int status);
+PD_API const char* pd_status_string(int status);
 
 /* One decode step on the device: out = softmax(sm_scale * q K^T) V per query head, over the
  * pages the block table names.  Replaces paged_decode_triton
  * (pagedattn/triton_decode.py:285-377). */
-int pd_decode(const PdDecodeArgs* args);
+PD_API int pd_decode(const PdDecodeArgs* args);
 
 /* The same step for callers that hold q, block_table, seq_lens and out in HOST memory:
  * copies the three inputs into the device buffers named by `args` (which must be large
  * enough), runs pd_decode, copies `out` back and waits for the stream.  The KV pages stay
  * where they live, on the device.  No counterpart in the reference, whose callers pass
  * CUDA tensors. */
-int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
+PD_API int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
 
 /* Bytes of workspace pd_decode needs for these arguments (depends on sizes, dtype, kernel
  * and split count, not on data).  Replaces the reference's shape-keyed global scratch
  * (_Workspace, pagedattn/triton_decode.py:266-282) with caller-owned memory. */
-int pd_workspace_bytes(const PdDecodeArgs* args, uint64_t* bytes);
+PD_API int pd_workspace_bytes(const PdDecodeArgs* args, uint64_t* bytes);
 
 /* Which kernel pd_decode would run: PD_KERNEL_SIMPLE or PD_KERNEL_STREAM, or a negative
  * PD_ERR_* if the arguments are rejected.  Touches no device. */
-int pd_select_kernel(const PdDecodeArgs* args);
+PD_API int pd_select_kernel(const PdDecodeArgs* args);
 
 /* Split count heuristic for PD_KERNEL_SIMPLE.  Same signature and role as pick_num_splits
  * (pagedattn/triton_decode.py:248-263); the policy is sized for B200's 148 SMs. */
-int pd_pick_num_splits(int batch, int num_kv_heads, int max_seq_len, int sm_count, int block_n);
+PD_API int pd_pick_num_splits(int batch, int num_kv_heads, int max_seq_len, int sm_count, int block_n);
 
 /* Log-sum-exp merge of partial results (see PdMergeArgs). */
-int pd_merge(const PdMergeArgs* args);
+PD_API int pd_merge(const PdMergeArgs* args);
 
 /* Dense dequantised fp16 gather (see PdGatherArgs). */
-int pd_gather(const PdGatherArgs* args);
+PD_API int pd_gather(const PdGatherArgs* args);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,254 @@
+"""Python entry point of the decode path.
+
+``paged_decode`` keeps the call shape of the reference's launcher
+(``pagedattn/triton_decode.py:285-295``): ``(q, cache, out=None, block_n=64,
+num_splits=None, per_page_bt=True, num_warps=4, num_stages=3, sm_scale=None)``; it is
+also exported as ``paged_decode_triton`` so existing call sites keep working.  What it
+keeps of the reference's behaviour:
+
+* writes into ``out`` when given and returns it; allocates ``[B, Hq, D]`` in q's dtype
+  otherwise (``:309-310``);
+* ``sm_scale`` overrides ``head_dim ** -0.5`` and is never re-derived (``:298-299, 328``);
+* asserts ``q.shape[-1] == cache.shape.head_dim`` and ``block_n % block_size == 0``
+  (``:306-307``);
+* runs on torch's current CUDA stream, no autograd;
+* an explicit ``num_splits`` cuts every request's KV range by the reference's rule
+  (``:78-82``) and merges the partial results by log-sum-exp.
+
+What differs: ``num_splits=None`` never synchronises with the device (the reference
+calls ``seq_lens.max().item()``, ``:320-326``); ``per_page_bt``, ``num_warps`` and
+``num_stages`` are accepted and ignored (pages are always resolved once per page, and
+the CUDA kernels fix their own warp and stage counts); the split scratch is cached per
+(device, stream), not per shape.  All compute happens in the CUDA library behind the C
+ABI; there is no CPU or PyTorch fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from . import _cabi
+from .cache import PagedKVCache
+
+_ws_lock = threading.Lock()
+_ws_cache: dict[tuple[int, int], torch.Tensor] = {}
+
+STATS = {"decode_launches": 0}
+
+
+def pick_num_splits(batch: int, num_kv_heads: int, max_seq_len: int, sm_count: int, block_n: int) -> int:
+    """Split count for the one-CTA-per-(request, kv head, split) kernel.
+
+    Same signature and role as ``pagedattn/triton_decode.py:248-263``.  The policy is
+    re-derived for a 148-SM part (see ``pd_pick_num_splits`` in the C ABI); the streaming
+    kernel balances work by itself and does not need it.
+    """
+    return int(_cabi.load().pd_pick_num_splits(int(batch), int(num_kv_heads), int(max_seq_len),
+                                               int(sm_count), int(block_n)))
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    if nbytes == 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    with _ws_lock:
+        buf = _ws_cache.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _ws_cache[key] = buf
+    return buf
+
+
+def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *, block_n: int = 64,
+               num_splits: int | None = None, sm_scale: float | None = None, kernel: str = "auto",
+               result_f32: torch.Tensor | None = None, result_lse: torch.Tensor | None = None,
+               status: torch.Tensor | None = None, max_seq_len: int = 0,
+               sm_count: int = 0) -> _cabi.PdDecodeArgs:
+    """Validated argument block for ``pd_decode`` (no workspace attached yet)."""
+    if q.dim() != 3:
+        raise ValueError("q must be [batch, num_q_heads, head_dim]")
+    b, hq, d = q.shape
+    assert d == cache.shape.head_dim, f"q head_dim {d} != cache head_dim {cache.shape.head_dim}"
+    assert block_n % cache.block_size == 0, "BLOCK_N must be a multiple of the page size"
+    if hq != cache.shape.num_q_heads:
+        raise ValueError(f"q has {hq} heads, cache.shape says {cache.shape.num_q_heads}")
+    if q.dtype not in _cabi.IO_CODE:
+        raise ValueError(f"q dtype {q.dtype} not supported (fp16 or bf16)")
+    if q.stride(2) != 1:
+        raise ValueError("head_dim must be contiguous in q")
+    if b != cache.batch:
+        raise ValueError(f"q batch {b} != block_table rows {cache.batch}")
+    if kernel not in _cabi.KERNEL_CODE:
+        raise ValueError(f"kernel must be one of {sorted(_cabi.KERNEL_CODE)}")
+    args = _cabi.PdDecodeArgs()
+    _cabi.fill_cache_fields(args, cache)
+    if args.num_kv_heads != cache.shape.num_kv_heads or args.block_size != cache.block_size:
+        raise ValueError("cache tensors disagree with cache.shape / cache.block_size")
+    args.q = q.data_ptr()
+    args.q_stride_b, args.q_stride_h = q.stride(0), q.stride(1)
+    if out is not None:
+        if out.shape != q.shape or out.dtype != q.dtype or out.stride(2) != 1:
+            raise ValueError("out must match q in shape and dtype with head_dim contiguous")
+        args.out = out.data_ptr()
+        args.out_stride_b, args.out_stride_h = out.stride(0), out.stride(1)
+    args.io_dtype = _cabi.IO_CODE[q.dtype]
+    args.sm_scale = float(cache.shape.softmax_scale if sm_scale is None else sm_scale)
+    args.num_splits = 0 if num_splits is None else int(num_splits)
+    if args.num_splits < 0:
+        raise ValueError("num_splits must be positive or None")
+    args.block_n = int(block_n)
+    args.kernel = _cabi.KERNEL_CODE[kernel]
+    args.sm_count = int(sm_count)
+    args.max_seq_len = int(max_seq_len)
+    if (result_f32 is None) != (result_lse is None):
+        raise ValueError("result_f32 and result_lse go together")
+    if result_f32 is not None:
+        if (result_f32.dtype != torch.float32 or result_lse.dtype != torch.float32
+                or tuple(result_f32.shape) != (b, hq, d) or tuple(result_lse.shape) != (b, hq)
+                or not result_f32.is_contiguous() or not result_lse.is_contiguous()):
+            raise ValueError("result_f32 [B,Hq,D] and result_lse [B,Hq] must be contiguous fp32")
+        args.result_f32, args.result_lse = result_f32.data_ptr(), result_lse.data_ptr()
+    if status is not None:
+        if status.dtype != torch.int32 or status.numel() < 1:
+            raise ValueError("status must be an int32 tensor")
+        args.status = status.data_ptr()
+    return args
+
+
+def workspace_bytes(args: _cabi.PdDecodeArgs) -> int:
+    n = ctypes.c_uint64(0)
+    _cabi.check(_cabi.load().pd_workspace_bytes(ctypes.byref(args), ctypes.byref(n)), "pd_workspace_bytes")
+    return int(n.value)
+
+
+def selected_kernel(args: _cabi.PdDecodeArgs) -> str:
+    rc = _cabi.load().pd_select_kernel(ctypes.byref(args))
+    if rc < 0:
+        _cabi.check(rc, "pd_select_kernel")
+    return _cabi.KERNEL_NAME[rc]
+
+
+def paged_decode(
+    q: torch.Tensor,
+    cache: PagedKVCache,
+    out: torch.Tensor | None = None,
+    block_n: int = 64,
+    num_splits: int | None = None,
+    per_page_bt: bool = True,
+    num_warps: int = 4,
+    num_stages: int = 3,
+    sm_scale: float | None = None,
+    *,
+    kernel: str = "auto",
+    result_f32: torch.Tensor | None = None,
+    result_lse: torch.Tensor | None = None,
+    status: torch.Tensor | None = None,
+    max_seq_len: int = 0,
+) -> torch.Tensor:
+    """Paged GQA decode attention: q ``[B, Hq, D]`` (fp16/bf16) -> ``[B, Hq, D]``.
+
+    Keyword-only extras: ``kernel`` ("auto", "simple", "stream") pins the CUDA kernel;
+    ``result_f32``/``result_lse`` additionally receive the fp32 result and its base-2
+    log-sum-exp (what a cross-GPU merge needs); ``status`` is an int32 device word that
+    collects the kernels' PD_DEV_* flags; ``max_seq_len`` is an optional host-side bound
+    on ``seq_lens`` that refines the automatic split count.
+    """
+    del per_page_bt, num_warps, num_stages
+    if not q.is_cuda:
+        raise _cabi.NativeLibraryError("paged_decode runs on CUDA tensors only; there is no CPU path")
+    if out is None:
+        out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
+    args = build_args(q, cache, out, block_n=block_n, num_splits=num_splits, sm_scale=sm_scale,
+                      kernel=kernel, result_f32=result_f32, result_lse=result_lse, status=status,
+                      max_seq_len=max_seq_len)
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, workspace_bytes(args))
+        if ws is not None:
+            args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        _cabi.check(_cabi.load().pd_decode(ctypes.byref(args)), "pd_decode")
+    STATS["decode_launches"] += 1
+    return out
+
+
+# Drop-in name of the reference's entry point (pagedattn/triton_decode.py:285).
+paged_decode_triton = paged_decode
+
+
+def merge_partials(part_out: torch.Tensor, part_lse: torch.Tensor, out: torch.Tensor | None = None,
+                   *, io_dtype: torch.dtype = torch.float16, want_f32: bool = False):
+    """Merge ``P`` partial results by log-sum-exp on the GPU.
+
+    ``part_out`` is ``[P, B, Hq, D]`` fp32 (each normalised), ``part_lse`` ``[P, B, Hq]``
+    fp32 in base 2, ``-inf`` for an empty partial; ``P`` may be splits of one GPU or the
+    ranks of a KV-range-sharded group.  Returns ``out`` (``[B, Hq, D]`` in ``io_dtype``),
+    or ``(out, merged_f32, merged_lse)`` when ``want_f32``.
+    """
+    if not part_out.is_cuda:
+        raise _cabi.NativeLibraryError("merge_partials runs on CUDA tensors only")
+    p, b, hq, d = part_out.shape
+    # each partial must be dense; the partials themselves may be any distance apart
+    if p and not part_out[0].is_contiguous():
+        part_out = part_out.contiguous()
+    if p and not part_lse[0].is_contiguous():
+        part_lse = part_lse.contiguous()
+    if out is None:
+        out = torch.empty((b, hq, d), dtype=io_dtype, device=part_out.device)
+    if not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    m = _cabi.PdMergeArgs()
+    m.part_out, m.part_lse = part_out.data_ptr(), part_lse.data_ptr()
+    m.out_stride_p, m.out_stride_row = part_out.stride(0), d
+    m.lse_stride_p, m.lse_stride_row = part_lse.stride(0), 1
+    m.num_parts, m.num_rows, m.head_dim = p, b * hq, d
+    m.out, m.dst_stride_row, m.io_dtype = out.data_ptr(), d, _cabi.IO_CODE[out.dtype]
+    f32 = lse = None
+    if want_f32:
+        f32 = torch.empty((b, hq, d), dtype=torch.float32, device=part_out.device)
+        lse = torch.empty((b, hq), dtype=torch.float32, device=part_out.device)
+        m.result_f32, m.result_lse = f32.data_ptr(), lse.data_ptr()
+    m.stream = torch.cuda.current_stream(part_out.device).cuda_stream
+    with torch.cuda.device(part_out.device):
+        _cabi.check(_cabi.load().pd_merge(ctypes.byref(m)), "pd_merge")
+    return (out, f32, lse) if want_f32 else out
+
+
+class HostDecoder:
+    """Decode steps for callers whose q, block table, lengths and result live in host memory.
+
+    Owns device staging buffers for the per-step inputs and the output; the KV pages are
+    device state and stay on the GPU.  ``step`` goes through ``pd_decode_host``: three
+    host-to-device copies, the decode, one device-to-host copy, one stream wait.
+    """
+
+    def __init__(self, cache: PagedKVCache, io_dtype: torch.dtype = torch.float16,
+                 sm_scale: float | None = None, kernel: str = "auto"):
+        dev = cache.k_cache.device
+        b, hq, d = cache.batch, cache.shape.num_q_heads, cache.shape.head_dim
+        self.q_dev = torch.empty((b, hq, d), dtype=io_dtype, device=dev)
+        self.out_dev = torch.empty_like(self.q_dev)
+        self.cache = cache
+        self.args = build_args(self.q_dev, cache, self.out_dev, sm_scale=sm_scale, kernel=kernel)
+        with torch.cuda.device(dev):
+            self.ws = _workspace(dev, workspace_bytes(self.args))
+        if self.ws is not None:
+            self.args.workspace, self.args.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        self.h2d_bytes = (self.q_dev.numel() * 2 + cache.block_table.numel() * 4 + cache.seq_lens.numel() * 4)
+        self.d2h_bytes = self.out_dev.numel() * 2
+
+    def step(self, q_host: torch.Tensor, block_table_host: torch.Tensor, seq_lens_host: torch.Tensor,
+             out_host: torch.Tensor) -> torch.Tensor:
+        for t in (q_host, block_table_host, seq_lens_host, out_host):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("host tensors must be contiguous CPU tensors")
+        io = _cabi.PdHostIO(q_host.data_ptr(), block_table_host.data_ptr(), seq_lens_host.data_ptr(),
+                            out_host.data_ptr())
+        dev = self.q_dev.device
+        self.args.stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            _cabi.check(_cabi.load().pd_decode_host(ctypes.byref(self.args), ctypes.byref(io)),
+                        "pd_decode_host")
+        return out_host

@@ -1,0 +1,128 @@
+"""Multi-GPU partitioning of the decode path: one process per GPU.
+
+Two schemes, neither present in the reference (a single-GPU kernel):
+
+* **Request sharding** — every (request, kv head) is independent
+  (pagedattn/triton_decode.py:10-12), so a ragged batch is split across ranks by
+  request, balanced by token count; each rank decodes the requests whose pages it holds
+  and nothing is exchanged.  ``partition_requests`` computes the assignment on the host.
+
+* **KV-range sharding** — for few, very long requests each rank holds a contiguous slice
+  of every request's tokens in its own page pool, decodes it to a normalised fp32 partial
+  plus its base-2 log-sum-exp, the ranks all-gather the partials (``B*Hq*(D+1)`` floats
+  per rank over NCCL/NVLink) and every rank merges them with the log-sum-exp merge kernel
+  — the same arithmetic that merges split-KV partials inside one GPU
+  (pagedattn/triton_decode.py:221-240).
+"""
+
+from __future__ import annotations
+
+import heapq
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import synth
+from .cache import PagedKVCache
+
+
+def partition_requests(seq_lens: Sequence[int], world: int) -> list[list[int]]:
+    """Token-balanced assignment of request indices to ``world`` ranks.
+
+    Longest-first greedy: the next longest request goes to the rank with the fewest
+    tokens so far (ties to the lower rank).  Deterministic; every request appears once.
+    """
+    if world <= 0:
+        raise ValueError("world must be positive")
+    heap = [(0, r) for r in range(world)]
+    heapq.heapify(heap)
+    shards: list[list[int]] = [[] for _ in range(world)]
+    for idx in sorted(range(len(seq_lens)), key=lambda i: (-int(seq_lens[i]), i)):
+        load, r = heapq.heappop(heap)
+        shards[r].append(idx)
+        heapq.heappush(heap, (load + int(seq_lens[idx]), r))
+    for s in shards:
+        s.sort()
+    return shards
+
+
+def token_ranges(seq_len: int, world: int, align: int) -> list[tuple[int, int]]:
+    """Contiguous [lo, hi) token slices of one request for ``world`` ranks.
+
+    Boundaries are multiples of ``align`` (the page size) so a page never straddles two
+    ranks; trailing ranks may get an empty slice when the request is short.
+    """
+    pages = -(-seq_len // align)
+    per = -(-pages // world)
+    out = []
+    for r in range(world):
+        lo = min(r * per * align, seq_len)
+        hi = min((r + 1) * per * align, seq_len)
+        out.append((lo, hi))
+    return out
+
+
+def make_kv_range_shard(name: str, rank: int, world: int, device, seed: int = 0,
+                        batch: int | None = None, seq_len: int | None = None):
+    """This rank's slice of a KV-range-sharded synthetic workload.
+
+    All ranks share q (drawn from ``seed``); rank r's pool holds tokens
+    ``token_ranges(seq_len, world, page)[r]`` of every request, drawn from ``seed + 1 + r``.
+    """
+    w = synth.WORKLOADS[name]
+    full = int(synth.draw_lengths(name, torch.Generator().manual_seed(seed), batch, seq_len)[0])
+    lo, hi = token_ranges(full, world, w.page)[rank]
+    q, _ = synth.make(name, device=device, seed=seed, batch=batch, seq_len=w.page)
+    _, cache = synth.make(name, device=device, seed=seed + 1 + rank, batch=batch, seq_len=max(hi - lo, 0))
+    return q, cache
+
+
+def _cuda_decode(q: torch.Tensor, cache: PagedKVCache, f32: torch.Tensor, lse: torch.Tensor,
+                 kernel: str) -> None:
+    from .decode import paged_decode
+
+    paged_decode(q, cache, result_f32=f32, result_lse=lse, kernel=kernel)
+
+
+def _cuda_merge(parts: torch.Tensor, lses: torch.Tensor, out: torch.Tensor) -> None:
+    from .decode import merge_partials
+
+    merge_partials(parts, lses, out=out)
+
+
+class KVRangeShardedDecoder:
+    """Decode step of one rank of a KV-range-sharded group.
+
+    ``step()`` = local decode to (fp32 partial, lse) -> one all-gather -> merge of
+    ``world`` partials into ``out``.  The partial and its lse live in one flat buffer so a
+    single collective moves both.  ``decode_fn``/``merge_fn`` default to the CUDA library;
+    host-side tests inject CPU stand-ins to exercise the plumbing over gloo.
+    """
+
+    def __init__(self, q: torch.Tensor, cache: PagedKVCache, group=None, kernel: str = "auto",
+                 decode_fn: Callable | None = None, merge_fn: Callable | None = None):
+        self.q, self.cache, self.group, self.kernel = q, cache, group, kernel
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        b, hq, d = q.shape
+        self.n_o = b * hq * d
+        self.local = torch.empty(self.n_o + b * hq, dtype=torch.float32, device=q.device)
+        self.f32 = self.local[: self.n_o].view(b, hq, d)
+        self.lse = self.local[self.n_o:].view(b, hq)
+        self.gathered = torch.empty((self.world, self.local.numel()), dtype=torch.float32, device=q.device)
+        self.out = torch.empty_like(q)
+        self.decode_fn = decode_fn or _cuda_decode
+        self.merge_fn = merge_fn or _cuda_merge
+        self.launches_per_step = 3  # decode, its split merge, the cross-rank merge
+
+    def step(self) -> torch.Tensor:
+        b, hq, d = self.q.shape
+        self.decode_fn(self.q, self.cache, self.f32, self.lse, self.kernel)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+        else:
+            self.gathered[0].copy_(self.local)
+        parts = self.gathered[:, : self.n_o].view(self.world, b, hq, d)
+        lses = self.gathered[:, self.n_o:].view(self.world, b, hq)
+        self.merge_fn(parts, lses, self.out)
+        return self.out

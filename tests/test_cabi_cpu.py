@@ -1,0 +1,131 @@
+"""CPU-side checks of the native boundary: the library loads, exports what the header
+declares, validates arguments without a device, and the host policies behave."""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+import re
+
+import pytest
+import torch
+
+import paged_decode_attention_b200 as pda
+from paged_decode_attention_b200 import _cabi, decode as pdec
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "paged_decode.h").read_text()
+    declared = set(re.findall(r"PD_API\s+[\w\s\*]+?\b(pd_\w+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = _cabi.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert declared == set(_cabi.EXPORTS)
+    assert lib.pd_abi_version() == _cabi.ABI_VERSION
+
+
+def test_struct_layout_matches_header_field_order():
+    header = (ROOT / "include" / "paged_decode.h").read_text()
+    body = header.split("typedef struct PdDecodeArgs {")[1].split("} PdDecodeArgs;")[0]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for stmt in body.split(";"):
+        stmt = stmt.strip()
+        if not stmt:
+            continue
+        for part in stmt.split(","):
+            names.append(re.findall(r"(\w+)\s*$", part.strip())[0])
+    assert names == [f[0] for f in _cabi.PdDecodeArgs._fields_]
+
+
+def test_status_strings():
+    assert _cabi.status_string(0) == "ok"
+    for rc in (-1, -2, -3, -4):
+        assert _cabi.status_string(rc) not in ("ok", "unknown status")
+
+
+def _cpu_case(hq=32, hkv=8, d=128, page=16, kv_dtype="fp16", b=2, s=100):
+    cache = pda.allocate(pda.ModelShape(hq, hkv, d, "t"), b, s, block_size=page, kv_dtype=kv_dtype,
+                         device="cpu", seed=1)
+    q = torch.zeros((b, hq, d), dtype=torch.float16)
+    return q, cache
+
+
+def test_validation_without_a_device():
+    lib = _cabi.load()
+    q, cache = _cpu_case()
+    args = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    assert lib.pd_select_kernel(ctypes.byref(args)) in (1, 2)
+    n = ctypes.c_uint64(123)
+    assert lib.pd_workspace_bytes(ctypes.byref(args), ctypes.byref(n)) == 0
+
+    bad = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    bad.num_q_heads = 30  # not a multiple of the kv heads
+    assert lib.pd_select_kernel(ctypes.byref(bad)) == -1
+    bad = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    bad.head_dim = 96
+    assert lib.pd_select_kernel(ctypes.byref(bad)) == -2
+    bad = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    bad.kv_dtype = 3  # int8 without scales
+    assert lib.pd_select_kernel(ctypes.byref(bad)) == -1
+    bad = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    bad.block_n = 24
+    assert lib.pd_select_kernel(ctypes.byref(bad)) == -1
+    assert lib.pd_select_kernel(None) == -1
+    assert lib.pd_decode(None) == -1 and lib.pd_merge(None) == -1 and lib.pd_gather(None) == -1
+
+
+def test_simple_kernel_workspace_grows_with_splits():
+    lib = _cabi.load()
+    q, cache = _cpu_case(b=2, s=4096)
+    sizes = []
+    for splits in (1, 2, 8):
+        args = pdec.build_args(q, cache, torch.empty_like(q), num_splits=splits, kernel="simple",
+                               sm_count=148)
+        n = ctypes.c_uint64(0)
+        assert lib.pd_workspace_bytes(ctypes.byref(args), ctypes.byref(n)) == 0
+        sizes.append(n.value)
+    assert sizes[0] == 0 and sizes[1] >= 2 * 2 * 32 * 129 * 4 and sizes[2] >= 4 * sizes[1] - 4096
+
+
+def test_python_entry_refuses_cpu_tensors():
+    q, cache = _cpu_case()
+    with pytest.raises(_cabi.NativeLibraryError):
+        pda.paged_decode(q, cache)
+    with pytest.raises(_cabi.NativeLibraryError):
+        pda.gather_contiguous(cache)
+
+
+def test_entry_point_asserts_like_the_reference():
+    q, cache = _cpu_case()
+    with pytest.raises(AssertionError):
+        pdec.build_args(q[:, :, :64], cache, None)
+    with pytest.raises(AssertionError):
+        pdec.build_args(q, cache, None, block_n=40)
+
+
+def test_pick_num_splits_policy():
+    f = pda.pick_num_splits
+    assert f(64, 8, 8192, 148, 64) >= 1
+    assert f(256, 8, 8192, 148, 64) == 1          # enough CTAs already
+    assert f(4, 8, 131072, 148, 64) > 8           # long context, few requests: split deep
+    assert f(1, 8, 128, 148, 64) == 1             # too short to split
+    assert f(1, 1, 10**6, 148, 64) <= 128
+    for b in (1, 3, 24, 100):
+        prev = None
+        for s in (64, 512, 4096, 32768, 262144):
+            n = f(b, 2, s, 148, 64)
+            assert n >= 1 and (prev is None or n >= prev)  # never fewer splits for longer context
+            assert n == 1 or s // n >= 4 * 64              # at least four tiles per split
+            prev = n
+    assert f(0, 8, 100, 148, 64) == 1 and f(4, 8, 100, 0, 64) == 1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_cabi, "_lib", None)
+    monkeypatch.setattr(_cabi, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.load()

@@ -1,0 +1,208 @@
+"""GPU parity of the CUDA decode path, called through the C ABI, against the golden
+outputs of the reference and the CPU oracle.
+
+Mirrors the reference's test list (tests/test_correctness.py): tile-edge lengths, split
+counts, quantized caches, page sizes, a ragged batch with length 1 and empty splits,
+group of one, shuffled vs ascending tables, other model shapes — for both CUDA kernels.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import helpers
+from oracle import c_oracle, paged_decode_oracle as po
+import paged_decode_attention_b200 as pda
+from paged_decode_attention_b200 import _cabi, decode as pdec
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = ("simple", "stream")
+
+
+def _run(case, kernel, num_splits, **kw):
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    args = pdec.build_args(q, cache, torch.empty_like(q), kernel="auto" if kernel == "stream" else kernel)
+    if kernel == "stream" and pdec.selected_kernel(args) != "stream":
+        pytest.skip("streaming kernel does not serve this shape")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = pda.paged_decode(q, cache, num_splits=num_splits, kernel=kernel, status=status, **kw)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return out
+
+
+@pytest.mark.parametrize("num_splits", [None, 1, 4])
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("case", cases.CASES, ids=lambda c: c.name)
+def test_matches_reference_golden(case, kernel, num_splits, golden):
+    out = _run(case, kernel, num_splits)
+    helpers.assert_close(out, golden[f"{case.name}/out_f32"], bf16=case.io_dtype == "bf16",
+                         what=f"{case.name}/{kernel}/splits={num_splits}")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", ["llama8b_fp8_e5m2_s2048", "llama8b_int8_s2048", "llama8b_b2_s4097"])
+def test_eight_splits(name, kernel, golden):
+    """tests/test_correctness.py:64-70 runs the quantized caches with 8 splits."""
+    out = _run(cases.BY_NAME[name], kernel, 8)
+    helpers.assert_close(out, golden[f"{name}/out_f32"], what=name)
+
+
+@pytest.mark.parametrize("case", cases.CASES, ids=lambda c: c.name)
+def test_gather_bit_exact(case, golden):
+    """Block-table indexing and dequantisation of the CUDA address function, bit for bit."""
+    _, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    k, v = pda.gather_contiguous(cache)
+    torch.cuda.synchronize()
+    assert cases.sha256_valid_rows(k.cpu().numpy(), oc.seq_lens) == str(golden[f"{case.name}/k_sha"])
+    assert cases.sha256_valid_rows(v.cpu().numpy(), oc.seq_lens) == str(golden[f"{case.name}/v_sha"])
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_block_n_page_64(kernel, golden):
+    """tests/test_correctness.py:73-78 passes block_n = max(64, page)."""
+    case = cases.BY_NAME["llama8b_page64_s1000"]
+    out = _run(case, kernel, 4, block_n=64)
+    helpers.assert_close(out, golden[f"{case.name}/out_f32"], what="page64")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("kv_dtype,ceiling", [("int8", 0.02), ("fp8_e5m2", 0.15)])
+def test_quantization_accuracy(kv_dtype, ceiling, kernel):
+    """Quantized cache vs the fp16 cache of the same values (tests/test_correctness.py:125-145)."""
+    rng = np.random.Generator(np.random.PCG64(11))
+    shape = pda.LLAMA3_8B
+    pages, page, b = 128, 16, 2
+    raw = rng.standard_normal((2, b * pages, page, 8, 128), dtype=np.float32).astype(np.float16)
+    table = rng.permutation(b * pages).astype(np.int32).reshape(b, pages)
+    lens = np.full(b, pages * page, dtype=np.int32)
+    q_np = rng.standard_normal((b, 32, 128), dtype=np.float32).astype(np.float16)
+    oc16 = po.OracleCache(32, 8, 128, page, "fp16", raw[0], raw[1], None, None, table, lens)
+    ref = c_oracle.decode(q_np, oc16)
+    kq, ks = pda.quantize_kv(torch.from_numpy(raw[0]).cuda(), kv_dtype)
+    vq, vs = pda.quantize_kv(torch.from_numpy(raw[1]).cuda(), kv_dtype)
+    cache = pda.PagedKVCache(shape, page, kv_dtype, kq, vq, ks, vs,
+                             torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda())
+    out = pda.paged_decode(torch.from_numpy(q_np).cuda(), cache, kernel=kernel if kernel == "simple" else "auto")
+    _, rel = helpers.errors(out, ref)
+    assert rel < ceiling, f"{kv_dtype}: {rel:.4f}"
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_sm_scale_override_and_out_argument(kernel):
+    case = cases.BY_NAME["c2_mini"]
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(q_np.astype(np.float32), oc, sm_scale=0.05)
+    cache = helpers.to_device_cache(oc)
+    q = torch.from_numpy(q_np).cuda()
+    out = torch.full_like(q, 7.0)
+    got = pda.paged_decode(q, cache, out=out, sm_scale=0.05, kernel=kernel if kernel == "simple" else "auto")
+    assert got.data_ptr() == out.data_ptr()
+    helpers.assert_close(out, ref, what="sm_scale")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_strided_q_out_and_interleaved_kv_layout(kernel, golden):
+    """K and V as strided views of one [NB, 2, PAGE, H, D] allocation (the layout newer
+    serving engines use), q and out as slices of padded buffers."""
+    case = cases.BY_NAME["llama8b_b3_s300"]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    both = torch.stack([cache.k_cache, cache.v_cache], dim=1).contiguous()
+    cache.k_cache, cache.v_cache = both.unbind(1)
+    assert not cache.k_cache.is_contiguous()
+    qbuf = torch.zeros((5, 40, 128), dtype=torch.float16, device="cuda")
+    obuf = torch.zeros_like(qbuf)
+    qbuf[:3, 4:36] = torch.from_numpy(q_np).cuda()
+    out = pda.paged_decode(qbuf[:3, 4:36], cache, out=obuf[:3, 4:36], kernel=kernel if kernel == "simple" else "auto")
+    helpers.assert_close(out, golden[f"{case.name}/out_f32"], what="strided")
+    assert float(obuf[3:].abs().max()) == 0.0 and float(obuf[:, :4].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("num_splits", [None, 3])
+def test_zero_length_requests_give_zero_rows(kernel, num_splits):
+    case = cases.Case("zeros", 32, 8, 128, 16, "fp16", (0, 33, 0, 1), seed=23)
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(q_np.astype(np.float32), oc)
+    out = _run(case, kernel, num_splits)
+    assert float(out[0].abs().max()) == 0.0 and float(out[2].abs().max()) == 0.0
+    helpers.assert_close(out, ref, what="zero-length")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_bad_block_id_sets_status_and_does_not_touch_memory(kernel):
+    """An id outside the pool is reported through the status word and its page skipped."""
+    case = cases.BY_NAME["llama8b_b2_s65"]
+    q_np, oc = cases.build(case)
+    oc.block_table[1, 2] = oc.k_cache.shape[0] + 5
+    cache = helpers.to_device_cache(oc)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = pda.paged_decode(torch.from_numpy(q_np).cuda(), cache, status=status,
+                           kernel=kernel if kernel == "simple" else "auto")
+    torch.cuda.synchronize()
+    assert int(status.item()) & _cabi.DEV_BAD_BLOCK
+    assert not torch.isnan(out).any()
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", ["llama8b_ragged", "c4_mini", "c1_qwen05b"])
+def test_fp32_result_and_lse(name, kernel):
+    case = cases.BY_NAME[name]
+    q_np, oc = cases.build(case)
+    ref_o, ref_lse = c_oracle.decode(cases.q_as_f32(case, q_np), oc, want_lse=True)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    f32 = torch.empty(q.shape, dtype=torch.float32, device="cuda")
+    lse = torch.empty(q.shape[:2], dtype=torch.float32, device="cuda")
+    pda.paged_decode(q, cache, result_f32=f32, result_lse=lse, kernel=kernel if kernel == "simple" else "auto")
+    helpers.assert_close(f32, ref_o, what="fp32 result")
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 5e-3
+
+
+def test_merge_partials_matches_oracle():
+    rng = np.random.Generator(np.random.PCG64(77))
+    po_ = rng.standard_normal((5, 3, 14, 64), dtype=np.float32)
+    pl = (rng.standard_normal((5, 3, 14), dtype=np.float32) * 6).astype(np.float32)
+    pl[2] = -np.inf            # an empty partial
+    pl[:, 1, 3] = -np.inf      # a row with nothing at all
+    want_o, want_l = po.merge_partials(po_, pl)
+    out, f32, lse = pda.merge_partials(torch.from_numpy(po_).cuda(), torch.from_numpy(pl).cuda(), want_f32=True)
+    assert np.abs(f32.cpu().numpy() - want_o).max() < 1e-5
+    assert np.array_equal(np.isneginf(lse.cpu().numpy()), np.isneginf(want_l))
+    fin = np.isfinite(want_l)
+    assert np.abs(lse.cpu().numpy()[fin] - want_l[fin]).max() < 1e-4
+    assert np.abs(out.float().cpu().numpy() - want_o).max() < 2e-3
+
+
+def test_host_buffer_entry_point_equals_device_call(golden):
+    case = cases.BY_NAME["c1_qwen05b"]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    dec = pda.HostDecoder(cache)
+    out_host = torch.empty((case.batch, case.hq, case.d), dtype=torch.float16).pin_memory()
+    dec.step(torch.from_numpy(q_np).pin_memory(), torch.from_numpy(oc.block_table).pin_memory(),
+             torch.from_numpy(oc.seq_lens).pin_memory(), out_host)
+    helpers.assert_close(out_host, golden[f"{case.name}/out_f32"], what="host entry")
+
+
+def test_rejects_bad_arguments_without_launching():
+    case = cases.BY_NAME["llama8b_b2_s64"]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = torch.from_numpy(q_np).cuda()
+    with pytest.raises(AssertionError):
+        pda.paged_decode(q, cache, block_n=24)
+    with pytest.raises(AssertionError):
+        pda.paged_decode(q[:, :, :64], cache)
+    args = pdec.build_args(q, cache, torch.empty_like(q), num_splits=4, kernel="simple")
+    assert _cabi.load().pd_decode(ctypes.byref(args)) == -3  # split scratch not supplied
