@@ -1,6 +1,1013 @@
+// Streaming decode kernel for sm_100a: a persistent grid of one CTA per SM.
+//
+// Work decomposition.  Every request's KV range (or every explicit split of it) for one block
+// of HB kv heads is a "virtual sequence" of 16-token tiles.  All virtual sequences are laid end
+// to end and the tile sequence is cut into equal contiguous shares, one per worker.  A worker
+// is HB consumer warps (one per kv head of the block) plus one producer warp; a CTA hosts
+// 8/HB workers (at most 4).  Shares are balanced to one tile whatever the length distribution,
+// and they are derived on the device from seq_lens, so the host never synchronises.
+//
+// Data movement.  The producer warp resolves each tile's page through the block table (32
+// tiles' entries are fetched with one coalesced load ahead of use) and issues tiled TMA loads
+// (cp.async.bulk.tensor) of the K and V boxes [HB heads][16 tokens][128 B] with the 128-byte
+// swizzle into a ring of shared-memory stages; completion is tracked by mbarriers
+// (full/empty per stage).  Per-(token, head) scales ride along as untiled bulk copies.  The
+// ring runs across request boundaries, so HBM requests never drain between requests.
+//
+// Math.  Each consumer warp keeps the (padded to 16) query rows of its group as mma A
+// fragments in registers, computes S = Q K^T with mma.sync m16n8k16 (K rows via ldmatrix, or
+// 16-byte shared loads plus in-register int8 / e5m2 -> f16 conversion), applies a base-2
+// online softmax with warp shuffles (the reference's recurrence,
+// pagedattn/triton_decode.py:159-166), and accumulates O += P V in fp32.  Scales factor out of
+// both contractions: S is multiplied by the K scale per token, P by the V scale per token, so
+// 8-bit pages are only ever converted, never multiplied element-wise.
+//
+// Results.  A (worker, virtual sequence) segment that covers a whole unsplit request writes
+// its output row directly; any other segment writes a normalised fp32 partial plus its base-2
+// log-sum-exp into slot (worker + virtual sequence) of the scratch, and the merge kernel
+// combines a request's slots (pagedattn/triton_decode.py:221-240).
+//
+// Every wait is bounded: a wait that exceeds its limit sets PD_DEV_TIMEOUT in the status word,
+// raises the CTA's abort flag, and all warps leave their loops; the producer then waits (again
+// bounded) for the copies it still has in flight before the CTA exits.
+#include <cuda.h>
+
+#include <mutex>
+#include <vector>
+
 #include "pd_stream.h"
+
 namespace pd {
-int stream_supports(const PdDecodeArgs*) { return PD_ERR_UNSUPPORTED; }
-uint64_t stream_workspace_bytes(const PdDecodeArgs*, int) { return 0; }
-int stream_run(const PdDecodeArgs*, Params&, int) { return PD_ERR_UNSUPPORTED; }
+
+// ---------------------------------------------------------------------------------------------
+// configuration
+// ---------------------------------------------------------------------------------------------
+constexpr int kTileTokens = 16;
+constexpr int kMaxVseq = 4096;
+constexpr int kMinTilesPerWorker = 4;
+constexpr int kSmemLimit = 227 * 1024;
+constexpr int kMaxStages = 12;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+template <int KV, int D, int HB, bool SCALED>
+struct StreamCfg {
+  static constexpr int EB = (KV == PD_KV_F16) ? 2 : 1;
+  static constexpr int ROWB = D * EB;
+  static_assert(ROWB == 128 || ROWB == 256, "row must be one or two 128-byte chunks");
+  static constexpr int NC = ROWB / 128;                     // 128-byte chunks per row
+  static constexpr int BOX_ELEMS = 128 / EB;                // elements of one chunk
+  static constexpr int WPC = (8 / HB) < 4 ? (8 / HB) : 4;   // workers per CTA
+  static constexpr int WARPS_PER_WORKER = HB + 1;
+  static constexpr int THREADS = WPC * WARPS_PER_WORKER * 32;
+  static constexpr int CHUNK_BYTES = HB * kTileTokens * 128; // one TMA box
+  static constexpr int TILE_BYTES = NC * CHUNK_BYTES;        // K (or V) of one tile
+  static constexpr int SCALE_BYTES = SCALED ? 2048 : 0;      // K scales at +0, V scales at +1024
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES + SCALE_BYTES;
+  static constexpr int KSTEPS = D / 16;
+  static constexpr int NT = D / 8;                           // output n-tiles
+};
+
+struct StreamParams {
+  Params p;
+  int32_t nvseq, nhb, splits, nstage;
+  uint32_t bar_off, meta_off, misc_off, prefix_off;
+  int32_t* plan;  // [0] tiles per worker, [1] total tiles, [2 + v] prefix of virtual sequence v
+  uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
+};
+
+struct MergeSlotsParams {
+  const int32_t* plan;
+  const float* part_o;
+  const float* part_lse;
+  int32_t batch, hq, group, hb_heads, splits, d;
+  void* out;
+  int64_t o_sb, o_sh;
+  float* res_o;
+  float* res_lse;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Waits for a barrier phase for at most kWaitLimitNs.  Returns false (after raising the CTA's
+// abort flag and PD_DEV_TIMEOUT) when it gives up or when another warp already aborted.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t* status,
+                                            volatile int* abort_flag, bool heed_abort) {
+  const unsigned long long t0 = global_timer_ns();
+  unsigned spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (heed_abort && *abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, PD_DEV_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status,
+                                          volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, abort_flag, true);
+}
+
+// Tiled TMA load of one 4-D box into shared memory; completion is counted on `bar`.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"((unsigned long long)src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t r;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
+  return r;
+}
+__device__ __forceinline__ float lds_half(uint32_t addr) {
+  unsigned short h;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+  return __half2float(__ushort_as_half(h));
+}
+// D(16x8, f32) += A(16x16, f16) * B(16x8, f16)
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Two stored 8-bit elements (bytes `lo_sel`, `lo_sel + 1` of w) -> packed f16x2, exactly.
+template <int KV>
+__device__ __forceinline__ uint32_t cvt_pair(uint32_t w, bool upper) {
+  if constexpr (KV == PD_KV_E5M2) {
+    // e5m2 is the high byte of an f16: place each byte above a zero byte
+    return __byte_perm(w, 0u, upper ? 0x3424u : 0x1404u);
+  } else {
+    // int8: w already holds x ^ 0x80 (= x + 128 as unsigned); 0x6400 | u is the f16 1024 + u,
+    // so subtracting 1152 leaves x
+    const uint32_t h = __byte_perm(w, 0x64646464u, upper ? 0x4342u : 0x4140u);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h),
+                              __half2half2(__ushort_as_half((unsigned short)0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// schedule helpers (shared by producer, consumers and the merge kernel)
+// ---------------------------------------------------------------------------------------------
+struct VseqInfo {
+  int hb, b, split, lo, hi;
+};
+
+__device__ __forceinline__ int clamp_len(const Params& p, int b) {
+  int len = __ldg(p.seq_lens + b);
+  const long long cap = (long long)p.max_blocks * p.page;
+  if (len < 0) len = 0;
+  if (len > cap) {
+    if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
+    len = (int)cap;
+  }
+  return len;
+}
+
+__device__ __forceinline__ VseqInfo vseq_info(const StreamParams& sp, int v) {
+  VseqInfo i;
+  i.split = v % sp.splits;
+  const int t = v / sp.splits;
+  i.b = t % sp.p.batch;
+  i.hb = t / sp.p.batch;
+  split_range(clamp_len(sp.p, i.b), i.split, sp.splits, sp.p.block_n, i.lo, i.hi);
+  return i;
+}
+
+// Largest v in [0, n) with prefix[v] <= g (prefix is non-decreasing, prefix[0] = 0, g < prefix[n]).
+__device__ __forceinline__ int find_vseq(const int* prefix, int n, int g) {
+  int lo = 0, hi = n;  // invariant: prefix[lo] <= g < prefix[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= g) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+// ---------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------
+template <int KV, int D, int HB, bool SCALED>
+__global__ void __launch_bounds__(StreamCfg<KV, D, HB, SCALED>::THREADS, 1)
+stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v) {
+  using C = StreamCfg<KV, D, HB, SCALED>;
+  constexpr unsigned kFull = 0xffffffffu;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  int* prefix = reinterpret_cast<int*>(smem + sp.prefix_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + sp.misc_off);
+
+  const Params& p = sp.p;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wl = warp / C::WARPS_PER_WORKER;    // worker within the CTA
+  const int role = warp % C::WARPS_PER_WORKER;  // < HB: consumer of that head; == HB: producer
+  const int nstage = sp.nstage;
+  const uint32_t stage0 = base + (uint32_t)wl * nstage * C::STAGE_BYTES;
+  const uint32_t full0 = base + sp.bar_off + (uint32_t)wl * nstage * 16;
+  const uint32_t empty0 = full0 + nstage * 8;
+  volatile int* meta = reinterpret_cast<volatile int*>(smem + sp.meta_off) + wl * nstage;
+
+  // ---- tiles per virtual sequence, then an inclusive scan: prefix[v] = first tile of v ------
+  const int nv = sp.nvseq;
+  for (int v = tid; v < nv; v += C::THREADS) {
+    const VseqInfo i = vseq_info(sp, v);
+    prefix[v + 1] = i.hi > i.lo ? (i.hi - i.lo + kTileTokens - 1) / kTileTokens : 0;
+  }
+  if (tid == 0) {
+    prefix[0] = 0;
+    *abort_flag = 0;
+  }
+  if (role == HB && lane == 0) {
+    for (int s = 0; s < nstage; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, HB);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int first = 1; first <= nv; first += 32) {
+      const int idx = first + lane;
+      int x = idx <= nv ? prefix[idx] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, x, o);
+        if (lane >= o) x += y;
+      }
+      if (idx <= nv) prefix[idx] = x + carry;
+      carry += __shfl_sync(kFull, x, 31);
+    }
+  }
+  __syncthreads();
+
+  const int total = prefix[nv];
+  const int workers = gridDim.x * C::WPC;
+  int per = (total + workers - 1) / workers;
+  if (per < kMinTilesPerWorker) per = kMinTilesPerWorker;
+  const int w = blockIdx.x * C::WPC + wl;  // global worker id
+  const long long g0l = (long long)w * per;
+  const int g0 = g0l < total ? (int)g0l : total;
+  const int g1 = g0 + per < total ? g0 + per : total;
+  if (blockIdx.x == 0) {
+    // the merge kernel re-derives every segment from this plan
+    if (tid == 0) {
+      sp.plan[0] = per;
+      sp.plan[1] = total;
+    }
+    for (int v = tid; v <= nv; v += C::THREADS) sp.plan[2 + v] = prefix[v];
+  }
+  if (g0 >= g1) return;  // nothing for this worker (no barrier is used after this point)
+
+  // =============================== producer warp =============================================
+  if (role == HB) {
+    constexpr uint32_t kTileTx = 2u * C::TILE_BYTES;
+    int it = 0;
+    int vbase = find_vseq(prefix, nv, g0);
+    bool aborted = false;
+    for (int g = g0; g < g1 && !aborted; g += 32) {
+      const int myg = g + lane;
+      const bool act = myg < g1;
+      int mv = vbase;
+      if (act)
+        while (prefix[mv + 1] <= myg) ++mv;
+      vbase = __shfl_sync(kFull, mv, 0);
+      int phys = 0, tok = 0, hbi = 0, bad = 0;
+      if (act) {
+        const VseqInfo i = vseq_info(sp, mv);
+        const int t0 = i.lo + (myg - prefix[mv]) * kTileTokens;
+        const int pg = t0 / p.page;
+        tok = t0 - pg * p.page;
+        hbi = i.hb;
+        phys = __ldg(p.block_table + (int64_t)i.b * p.bt_stride + pg);
+        if ((unsigned)phys >= (unsigned)p.num_blocks) {
+          if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
+          bad = 1;
+          phys = 0;
+        }
+      }
+      const int n = g1 - g < 32 ? g1 - g : 32;
+      for (int i = 0; i < n; ++i, ++it) {
+        const int st = it % nstage;
+        const uint32_t ph = (uint32_t)(it / nstage) & 1u;
+        const int phys_i = __shfl_sync(kFull, phys, i);
+        const int tok_i = __shfl_sync(kFull, tok, i);
+        const int hb_i = __shfl_sync(kFull, hbi, i);
+        const int bad_i = __shfl_sync(kFull, bad, i);
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(empty0 + 8 * st, ph ^ 1u, p.status, abort_flag) ? 1 : 0;
+          if (ok) {
+            const uint32_t fb = full0 + 8 * st;
+            const uint32_t dst = stage0 + (uint32_t)st * C::STAGE_BYTES;
+            meta[st] = bad_i;
+            if (bad_i) {
+              mbar_arrive(fb);  // consumers skip the tile
+            } else {
+              mbar_arrive_expect_tx(fb, kTileTx + (SCALED ? 2u * sp.scale_tx_bytes : 0u));
+#pragma unroll
+              for (int c = 0; c < C::NC; ++c) {
+                tma_load_4d(dst + c * C::CHUNK_BYTES, &tm_k, fb, c * C::BOX_ELEMS, tok_i,
+                            hb_i * HB, phys_i);
+                tma_load_4d(dst + C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, fb,
+                            c * C::BOX_ELEMS, tok_i, hb_i * HB, phys_i);
+              }
+              if constexpr (SCALED) {
+                const int64_t so = (int64_t)phys_i * p.sc_sb + (int64_t)tok_i * p.sc_st;
+                bulk_load(dst + 2 * C::TILE_BYTES, p.k_scale + so, sp.scale_tx_bytes, fb);
+                bulk_load(dst + 2 * C::TILE_BYTES + 1024, p.v_scale + so, sp.scale_tx_bytes, fb);
+              }
+            }
+          }
+        }
+        if (!__shfl_sync(kFull, ok, 0)) {
+          aborted = true;
+          break;
+        }
+      }
+    }
+    if (lane == 0 && (aborted || *abort_flag)) {
+      // give the copies still in flight a bounded chance to land before the CTA exits
+      for (int k = 1; k <= nstage && k <= it; ++k) {
+        const int ii = it - k;
+        mbar_wait_slow(full0 + 8 * (ii % nstage), (uint32_t)(ii / nstage) & 1u, nullptr,
+                       abort_flag, false);
+      }
+    }
+    return;
+  }
+
+  // =============================== consumer warps ============================================
+  const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
+  const int hg = HB * p.group;              // query heads of one head block
+  int it = 0;
+  int v = find_vseq(prefix, nv, g0);
+  int g = g0;
+  bool aborted = false;
+
+  while (g < g1 && !aborted) {
+    while (prefix[v + 1] <= g) ++v;
+    const VseqInfo vi = vseq_info(sp, v);
+    const int vend = prefix[v + 1];
+    const int seg_end = g1 < vend ? g1 : vend;
+    int j = g - prefix[v];
+    const bool whole = (j == 0) && (seg_end == vend) && (sp.splits == 1);
+    const int kvh = vi.hb * HB + role;
+
+    // ---- query rows of this kv head's group as A fragments (rows >= group are zero) ---------
+    uint32_t qa[C::KSTEPS][4];
+    {
+      const __half* qrow0 = (const __half*)p.q + (int64_t)vi.b * p.q_sb +
+                            (int64_t)(kvh * p.group + gq) * p.q_sh;
+      const __half* qrow1 = qrow0 + 8 * p.q_sh;
+      const bool r0 = gq < p.group, r1 = gq + 8 < p.group;
+#pragma unroll
+      for (int ks = 0; ks < C::KSTEPS; ++ks) {
+        int c_lo, c_hi;  // head_dim index of fragment columns (2tq, 2tq+1) and (2tq+8, 2tq+9)
+        if constexpr (KV == PD_KV_F16) {
+          c_lo = 16 * ks + 2 * tq;
+          c_hi = c_lo + 8;
+        } else {
+          // 8-bit rows are read as 16-byte chunks 2tq and 2tq+1; k-step ks uses word ks % 4 of
+          // chunk 2tq + ks / 4, whose four elements fill the thread's four k slots
+          c_lo = 32 * tq + 16 * (ks >> 2) + 4 * (ks & 3);
+          c_hi = c_lo + 2;
+        }
+        qa[ks][0] = r0 ? __ldg(reinterpret_cast<const uint32_t*>(qrow0 + c_lo)) : 0u;
+        qa[ks][1] = r1 ? __ldg(reinterpret_cast<const uint32_t*>(qrow1 + c_lo)) : 0u;
+        qa[ks][2] = r0 ? __ldg(reinterpret_cast<const uint32_t*>(qrow0 + c_hi)) : 0u;
+        qa[ks][3] = r1 ? __ldg(reinterpret_cast<const uint32_t*>(qrow1 + c_hi)) : 0u;
+      }
+    }
+
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[C::NT][4];
+#pragma unroll
+    for (int n = 0; n < C::NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    for (; g < seg_end; ++g, ++j, ++it) {
+      const int st = it % nstage;
+      if (!mbar_wait(full0 + 8 * st, (uint32_t)(it / nstage) & 1u, p.status, abort_flag)) {
+        aborted = true;
+        break;
+      }
+      if (meta[st] == 0) {
+        const uint32_t kbase = stage0 + (uint32_t)st * C::STAGE_BYTES + role * (kTileTokens * 128);
+        const uint32_t vbase = kbase + C::TILE_BYTES;
+        const int remaining = vi.hi - (vi.lo + j * kTileTokens);
+        const int valid = remaining < kTileTokens ? remaining : kTileTokens;
+
+        // ---- S = Q K^T: two 8-token n-tiles ---------------------------------------------
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        if constexpr (KV == PD_KV_F16) {
+          // lane l addresses row (token) of 8x8 matrix l/8: matrices (nt0, lo), (nt0, hi),
+          // (nt1, lo), (nt1, hi) where lo/hi are the two 16-byte chunks of the k-step
+          const int mi = lane >> 3;
+          const int token = 8 * (mi >> 1) + (lane & 7);
+          const uint32_t row = kbase + token * 128;
+#pragma unroll
+          for (int ks = 0; ks < C::KSTEPS; ++ks) {
+            const int chunk = ((2 * ks) & 7) + (mi & 1);
+            uint32_t b[4];
+            ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
+            mma_f16(s[0], qa[ks], b[0], b[1]);
+            mma_f16(s[1], qa[ks], b[2], b[3]);
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int token = 8 * nt + gq;
+            const uint32_t row = kbase + token * 128;
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh) {
+              uint32_t wv[4];
+              lds128(row + (((2 * tq + jh) ^ (token & 7)) << 4), wv);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t x = KV == PD_KV_I8 ? wv[i] ^ 0x80808080u : wv[i];
+                mma_f16(s[nt], qa[4 * jh + i], cvt_pair<KV>(x, false), cvt_pair<KV>(x, true));
+              }
+            }
+          }
+        }
+
+        // ---- scale, mask, online softmax ------------------------------------------------
+        float vsc[2][2];  // V scale of the thread's four tokens
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int token = 8 * nt + 2 * tq + e;
+            float f = p.scale_log2;
+            vsc[nt][e] = 1.f;
+            if constexpr (SCALED) {
+              const uint32_t sa = stage0 + (uint32_t)st * C::STAGE_BYTES + 2 * C::TILE_BYTES +
+                                  (token * p.hkv + kvh) * 2;
+              f *= lds_half(sa);
+              vsc[nt][e] = lds_half(sa + 1024) * 256.f;
+            }
+            const bool live = token < valid;
+            s[nt][e] = live ? s[nt][e] * f : -INFINITY;
+            s[nt][2 + e] = live ? s[nt][2 + e] * f : -INFINITY;
+          }
+        }
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: token 0 is live
+        const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+        uint32_t pa[4];
+        {
+          float pr[2][4];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float x0 = fast_exp2(s[nt][e] - mn0);
+              const float x1 = fast_exp2(s[nt][2 + e] - mn1);
+              ps0 += x0;
+              ps1 += x1;
+              pr[nt][e] = x0 * vsc[nt][e];
+              pr[nt][2 + e] = x1 * vsc[nt][e];
+            }
+          }
+          pa[0] = pack_half2(pr[0][0], pr[0][1]);  // row gq,     tokens 2tq, 2tq+1
+          pa[1] = pack_half2(pr[0][2], pr[0][3]);  // row gq + 8
+          pa[2] = pack_half2(pr[1][0], pr[1][1]);  // row gq,     tokens 2tq+8, 2tq+9
+          pa[3] = pack_half2(pr[1][2], pr[1][3]);
+        }
+        l0 = l0 * a0 + ps0;
+        l1 = l1 * a1 + ps1;
+#pragma unroll
+        for (int n = 0; n < C::NT; ++n) {
+          o[n][0] *= a0;
+          o[n][1] *= a0;
+          o[n][2] *= a1;
+          o[n][3] *= a1;
+        }
+
+        // ---- O += P V -----------------------------------------------------------------------
+        // rows of V past `valid` hold whatever the page holds: zero them so 0 * NaN cannot occur
+        uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2tq,2tq+1), (+8,+9)
+        if (valid < kTileTokens) {
+          keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
+          keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
+        }
+        if constexpr (KV == PD_KV_F16) {
+          // transposed 8x8 matrices: (tokens 0-7, chunk nd), (8-15, nd), (0-7, nd+1), (8-15, nd+1)
+          const int mi = lane >> 3;
+          const int token = 8 * (mi & 1) + (lane & 7);
+          const uint32_t row = vbase + token * 128;
+#pragma unroll
+          for (int nd = 0; nd < C::NT; nd += 2) {
+            const int chunk = (nd & 7) + (mi >> 1);
+            uint32_t b[4];
+            ldmatrix_x4_trans(row + (nd >> 3) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
+            mma_f16(o[nd], pa, b[0] & keep_lo, b[1] & keep_hi);
+            mma_f16(o[nd + 1], pa, b[2] & keep_lo, b[3] & keep_hi);
+          }
+        } else {
+          // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of columns
+          // 4*(gq + 8*jj) .. +3 and transposes bytes in registers.  Output n-tile 4*jj + i then
+          // holds head_dim column 32*jj + 4*c + i for fragment column c; the epilogue undoes it.
+          const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
+#pragma unroll
+          for (int jj = 0; jj < D / 32; ++jj) {
+            uint32_t r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int chunk = 2 * jj + (gq >> 2);
+              r[k] = lds32(vbase + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) + ((gq & 3) << 2));
+              if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
+            }
+            // bytes (c0, c2) and (c1, c3) of the token pairs side by side
+            const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
+            const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
+            mma_f16(o[4 * jj + 0], pa, cvt_pair<KV>(e01, false) & keep_lo, cvt_pair<KV>(e23, false) & keep_hi);
+            mma_f16(o[4 * jj + 1], pa, cvt_pair<KV>(o01, false) & keep_lo, cvt_pair<KV>(o23, false) & keep_hi);
+            mma_f16(o[4 * jj + 2], pa, cvt_pair<KV>(e01, true) & keep_lo, cvt_pair<KV>(e23, true) & keep_hi);
+            mma_f16(o[4 * jj + 3], pa, cvt_pair<KV>(o01, true) & keep_lo, cvt_pair<KV>(o23, true) & keep_hi);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * st);
+    }
+    if (aborted) break;
+
+    // ---- segment epilogue ---------------------------------------------------------------------
+    l0 += __shfl_xor_sync(kFull, l0, 1);
+    l0 += __shfl_xor_sync(kFull, l0, 2);
+    l1 += __shfl_xor_sync(kFull, l1, 1);
+    l1 += __shfl_xor_sync(kFull, l1, 2);
+    const float unscale = SCALED ? (1.f / 256.f) : 1.f;
+    const float inv0 = l0 > 0.f ? unscale / l0 : 0.f, inv1 = l1 > 0.f ? unscale / l1 : 0.f;
+    const float lse0 = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
+    const float lse1 = l1 > 0.f ? m1 + log2f(l1) : -INFINITY;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int rrow = gq + 8 * half;
+      if (rrow >= p.group) continue;
+      const float inv = half ? inv1 : inv0;
+      const float lse = half ? lse1 : lse0;
+      const int hq = kvh * p.group + rrow;
+      __half* dst16 = nullptr;
+      float* dst32 = nullptr;
+      if (whole) {
+        if (p.out) dst16 = (__half*)p.out + (int64_t)vi.b * p.o_sb + (int64_t)hq * p.o_sh;
+        if (p.res_o) {
+          dst32 = p.res_o + ((int64_t)vi.b * p.hq + hq) * D;
+          if (tq == 0) p.res_lse[(int64_t)vi.b * p.hq + hq] = lse;
+        }
+      } else {
+        const int64_t slot_row = (int64_t)(w + v) * hg + role * p.group + rrow;
+        dst32 = p.part_o + slot_row * D;
+        if (tq == 0) p.part_lse[slot_row] = lse;
+      }
+      if constexpr (KV == PD_KV_F16) {
+#pragma unroll
+        for (int n = 0; n < C::NT; ++n) {
+          const int col = 8 * n + 2 * tq;
+          const float x = o[n][2 * half] * inv, y = o[n][2 * half + 1] * inv;
+          if (dst16) *reinterpret_cast<__half2*>(dst16 + col) = __floats2half2_rn(x, y);
+          if (dst32) *reinterpret_cast<float2*>(dst32 + col) = make_float2(x, y);
+        }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < D / 32; ++jj) {
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            e[i] = o[4 * jj + i][2 * half] * inv;          // fragment column 2tq
+            e[4 + i] = o[4 * jj + i][2 * half + 1] * inv;  // fragment column 2tq + 1
+          }
+          const int col = 32 * jj + 8 * tq;
+          if (dst16) {
+            uint4 pk;
+            pk.x = pack_half2(e[0], e[1]);
+            pk.y = pack_half2(e[2], e[3]);
+            pk.z = pack_half2(e[4], e[5]);
+            pk.w = pack_half2(e[6], e[7]);
+            *reinterpret_cast<uint4*>(dst16 + col) = pk;
+          }
+          if (dst32) {
+            *reinterpret_cast<float4*>(dst32 + col) = make_float4(e[0], e[1], e[2], e[3]);
+            *reinterpret_cast<float4*>(dst32 + col + 4) = make_float4(e[4], e[5], e[6], e[7]);
+          }
+        }
+      }
+    }
+    ++v;
+  }
+}
+
+// One CTA per (request, query head): merges the slots the plan assigns to the request.  Rows
+// a single unsplit segment covered were written by the decode kernel and are left alone; rows
+// with no tokens become zero.
+__global__ void __launch_bounds__(128) stream_merge_kernel(const MergeSlotsParams mp) {
+  const int row = blockIdx.x;
+  const int b = row / mp.hq, hq = row % mp.hq;
+  const int kvh = hq / mp.group;
+  const int hb = kvh / mp.hb_heads;
+  const int hl = (kvh % mp.hb_heads) * mp.group + hq % mp.group;
+  const int hg = mp.hb_heads * mp.group;
+  const int per = mp.plan[0];
+  const int32_t* prefix = mp.plan + 2;
+  const int v0 = (hb * mp.batch + b) * mp.splits;
+
+  float m = -INFINITY;
+  int count = 0;
+  for (int s = 0; s < mp.splits; ++s) {
+    const int v = v0 + s;
+    const int first = prefix[v], last = prefix[v + 1];
+    if (last <= first) continue;
+    for (int wk = first / per; wk <= (last - 1) / per; ++wk) {
+      m = fmaxf(m, mp.part_lse[(int64_t)(wk + v) * hg + hl]);
+      ++count;
+    }
+  }
+  if (count == 1 && mp.splits == 1) return;
+  float denom = 0.f;
+  if (count > 0 && m > -INFINITY) {
+    for (int s = 0; s < mp.splits; ++s) {
+      const int v = v0 + s;
+      const int first = prefix[v], last = prefix[v + 1];
+      if (last <= first) continue;
+      for (int wk = first / per; wk <= (last - 1) / per; ++wk)
+        denom += exp2f(mp.part_lse[(int64_t)(wk + v) * hg + hl] - m);
+    }
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int d = threadIdx.x; d < mp.d; d += blockDim.x) {
+    float acc = 0.f;
+    if (denom > 0.f) {
+      for (int s = 0; s < mp.splits; ++s) {
+        const int v = v0 + s;
+        const int first = prefix[v], last = prefix[v + 1];
+        if (last <= first) continue;
+        for (int wk = first / per; wk <= (last - 1) / per; ++wk) {
+          const int64_t sr = (int64_t)(wk + v) * hg + hl;
+          const float lse = mp.part_lse[sr];
+          if (lse > -INFINITY) acc += exp2f(lse - m) * mp.part_o[sr * mp.d + d];
+        }
+      }
+    }
+    const float x = acc * inv;
+    if (mp.out) ((__half*)mp.out)[(int64_t)b * mp.o_sb + (int64_t)hq * mp.o_sh + d] = __float2half_rn(x);
+    if (mp.res_o) mp.res_o[(int64_t)row * mp.d + d] = x;
+  }
+  if (threadIdx.x == 0 && mp.res_lse) mp.res_lse[row] = denom > 0.f ? m + log2f(denom) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static uint64_t round_up64(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+static int head_block(int hkv) {
+  for (int hb = 8; hb > 1; hb >>= 1)
+    if (hkv % hb == 0) return hb;
+  return 1;
+}
+
+struct Shape {
+  int hb, nhb, wpc, splits, nvseq, stage_bytes, threads;
+  bool scaled;
+};
+
+static Shape derive(const PdDecodeArgs* a) {
+  Shape s;
+  s.hb = head_block(a->num_kv_heads);
+  s.nhb = a->num_kv_heads / s.hb;
+  s.wpc = 8 / s.hb < 4 ? 8 / s.hb : 4;
+  s.splits = a->num_splits > 0 ? a->num_splits : 1;
+  const long long nv = (long long)s.nhb * a->batch * s.splits;
+  s.nvseq = nv > INT32_MAX ? INT32_MAX : (int)nv;
+  s.scaled = a->k_scale != nullptr;
+  const int eb = a->kv_dtype == PD_KV_F16 ? 2 : 1;
+  const int nc = a->head_dim * eb / 128;
+  s.stage_bytes = 2 * nc * s.hb * kTileTokens * 128 + (s.scaled ? 2048 : 0);
+  s.threads = s.wpc * (s.hb + 1) * 32;
+  return s;
+}
+
+struct SmemPlan {
+  int nstage;
+  uint32_t bar_off, meta_off, misc_off, prefix_off, total;
+};
+
+static bool plan_smem(const Shape& s, SmemPlan& sm) {
+  const uint32_t fixed_per_stage = (uint32_t)s.wpc * (16 + 4);
+  const uint32_t tail = 64 + (uint32_t)(s.nvseq + 2) * 4 + 1024 /* alignment slack */;
+  int n = kMaxStages;
+  for (; n >= 2; --n) {
+    const uint64_t need = (uint64_t)n * s.wpc * s.stage_bytes + (uint64_t)n * fixed_per_stage + tail;
+    if (need <= (uint64_t)kSmemLimit) break;
+  }
+  if (n < 2) return false;
+  sm.nstage = n;
+  sm.bar_off = (uint32_t)n * s.wpc * s.stage_bytes;
+  sm.meta_off = sm.bar_off + (uint32_t)n * s.wpc * 16;
+  sm.misc_off = (sm.meta_off + (uint32_t)n * s.wpc * 4 + 15u) & ~15u;
+  sm.prefix_off = sm.misc_off + 16;
+  sm.total = sm.prefix_off + (uint32_t)(s.nvseq + 2) * 4 + 1024;
+  return true;
+}
+
+int stream_supports(const PdDecodeArgs* a) {
+  if (a->io_dtype != PD_IO_F16) return PD_ERR_UNSUPPORTED;
+  if (a->kv_dtype == PD_KV_BF16) return PD_ERR_UNSUPPORTED;
+  const int eb = a->kv_dtype == PD_KV_F16 ? 2 : 1;
+  const int rowb = a->head_dim * eb;
+  if (rowb != 128 && rowb != 256) return PD_ERR_UNSUPPORTED;
+  if (a->batch <= 0) return PD_ERR_UNSUPPORTED;
+  const int group = a->num_q_heads / a->num_kv_heads;
+  if (group > 16) return PD_ERR_UNSUPPORTED;
+  if (a->block_size % kTileTokens != 0 || a->block_size > 256) return PD_ERR_UNSUPPORTED;
+  const int block_n = a->block_n ? a->block_n : 64;
+  if (block_n % kTileTokens != 0) return PD_ERR_UNSUPPORTED;
+  // 32-bit fragment loads of q, vector stores of out
+  if (((uintptr_t)a->q % 4) || a->q_stride_b % 2 || a->q_stride_h % 2) return PD_ERR_UNSUPPORTED;
+  if (a->out && (((uintptr_t)a->out % 16) || a->out_stride_b % 8 || a->out_stride_h % 8))
+    return PD_ERR_UNSUPPORTED;
+  if (a->result_f32 && (((uintptr_t)a->result_f32 % 16) || ((uintptr_t)a->result_lse % 4)))
+    return PD_ERR_UNSUPPORTED;
+  if (a->k_scale) {
+    if (a->scale_stride_token != a->num_kv_heads || (a->scale_stride_block * 2) % 16 ||
+        ((uintptr_t)a->k_scale % 16) || ((uintptr_t)a->v_scale % 16) || a->num_kv_heads > 32)
+      return PD_ERR_UNSUPPORTED;
+  }
+  const Shape s = derive(a);
+  if ((long long)s.nhb * a->batch * s.splits > kMaxVseq) return PD_ERR_UNSUPPORTED;
+  SmemPlan sm;
+  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  // tensor-map limits
+  if ((uint64_t)a->kv_stride_block * eb >= (1ull << 40) || (uint64_t)a->kv_stride_token * eb >= (1ull << 40) ||
+      (uint64_t)a->kv_stride_head * eb >= (1ull << 40))
+    return PD_ERR_UNSUPPORTED;
+  return PD_OK;
+}
+
+struct WorkspaceLayout {
+  uint64_t plan_off, lse_off, o_off, total;
+  int slots;
+};
+
+static WorkspaceLayout workspace_layout(const PdDecodeArgs* a, const Shape& s, int sm_count) {
+  WorkspaceLayout w;
+  const int group = a->num_q_heads / a->num_kv_heads;
+  w.slots = sm_count * s.wpc + s.nvseq;
+  w.plan_off = 0;
+  w.lse_off = round_up64((uint64_t)(s.nvseq + 3) * 4, 256);
+  w.o_off = w.lse_off + round_up64((uint64_t)w.slots * s.hb * group * 4, 256);
+  w.total = w.o_off + round_up64((uint64_t)w.slots * s.hb * group * a->head_dim * 4, 256);
+  return w;
+}
+
+uint64_t stream_workspace_bytes(const PdDecodeArgs* a, int sm_count) {
+  return workspace_layout(a, derive(a), sm_count).total;
+}
+
+// ---- tensor maps --------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return (EncodeFn)ptr;
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int64_t sb, st, sh;
+  int32_t d, page, hkv, nb, hb, kv;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && sb == o.sb && st == o.st && sh == o.sh && d == o.d && page == o.page &&
+           hkv == o.hkv && nb == o.nb && hb == o.hb && kv == o.kv;
+  }
+};
+
+// Tensor map over one cache tensor with dimensions ordered (head_dim, token, head, block) so
+// that a box lands in shared memory as [head][token][128 bytes]: a head's 16 token rows are
+// consecutive 128-byte rows and the 128-byte swizzle spreads them over all banks.
+static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::vector<std::pair<MapKey, CUtensorMap>> cache;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (auto& e : cache)
+      if (e.first == k) {
+        *out = e.second;
+        return true;
+      }
+  }
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  const int eb = k.kv == PD_KV_F16 ? 2 : 1;
+  const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
+  const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap m;
+  const CUresult r = enc(&m, eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+                         const_cast<void*>(k.base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= 64) cache.erase(cache.begin());
+    cache.emplace_back(k, m);
+  }
+  *out = m;
+  return true;
+}
+
+template <int KV, int D, int HB, bool SCALED>
+static cudaError_t launch_one(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                              int grid, uint32_t smem, cudaStream_t st) {
+  using C = StreamCfg<KV, D, HB, SCALED>;
+  auto* kern = stream_decode_kernel<KV, D, HB, SCALED>;
+  static bool configured[64] = {};  // per device: the opt-in shared-memory limit has been raised
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorInvalidDevice;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  kern<<<grid, C::THREADS, smem, st>>>(sp, mk, mv);
+  return cudaGetLastError();
+}
+
+template <int KV, int D, bool SCALED>
+static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                             int grid, uint32_t smem, cudaStream_t st) {
+  switch (hb) {
+    case 8: return launch_one<KV, D, 8, SCALED>(sp, mk, mv, grid, smem, st);
+    case 4: return launch_one<KV, D, 4, SCALED>(sp, mk, mv, grid, smem, st);
+    case 2: return launch_one<KV, D, 2, SCALED>(sp, mk, mv, grid, smem, st);
+    default: return launch_one<KV, D, 1, SCALED>(sp, mk, mv, grid, smem, st);
+  }
+}
+
+int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
+  const Shape s = derive(a);
+  SmemPlan sm;
+  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
+  if (!a->workspace || a->workspace_bytes < wl.total) return PD_ERR_WORKSPACE;
+
+  MapKey key{a->k_cache, a->kv_stride_block, a->kv_stride_token, a->kv_stride_head, a->head_dim,
+             a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
+  CUtensorMap mk, mv;
+  if (!get_tensor_map(key, &mk)) return PD_ERR_CUDA;
+  key.base = a->v_cache;
+  if (!get_tensor_map(key, &mv)) return PD_ERR_CUDA;
+
+  StreamParams sp;
+  sp.p = p;
+  sp.p.num_splits = s.splits;
+  sp.p.part_lse = (float*)((char*)a->workspace + wl.lse_off);
+  sp.p.part_o = (float*)((char*)a->workspace + wl.o_off);
+  sp.nvseq = s.nvseq;
+  sp.nhb = s.nhb;
+  sp.splits = s.splits;
+  sp.nstage = sm.nstage;
+  sp.bar_off = sm.bar_off;
+  sp.meta_off = sm.meta_off;
+  sp.misc_off = sm.misc_off;
+  sp.prefix_off = sm.prefix_off;
+  sp.plan = (int32_t*)((char*)a->workspace + wl.plan_off);
+  sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
+
+  const cudaStream_t st = (cudaStream_t)a->stream;
+  cudaError_t e;
+  if (a->kv_dtype == PD_KV_F16) {
+    e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else if (a->kv_dtype == PD_KV_E5M2) {
+    e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                 : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else {
+    e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  }
+  if (e != cudaSuccess) return PD_ERR_CUDA;
+
+  MergeSlotsParams mp;
+  mp.plan = sp.plan;
+  mp.part_o = sp.p.part_o;
+  mp.part_lse = sp.p.part_lse;
+  mp.batch = a->batch;
+  mp.hq = a->num_q_heads;
+  mp.group = a->num_q_heads / a->num_kv_heads;
+  mp.hb_heads = s.hb;
+  mp.splits = s.splits;
+  mp.d = a->head_dim;
+  mp.out = a->out;
+  mp.o_sb = a->out_stride_b;
+  mp.o_sh = a->out_stride_h;
+  mp.res_o = a->result_f32;
+  mp.res_lse = a->result_lse;
+  stream_merge_kernel<<<a->batch * a->num_q_heads, 128, 0, st>>>(mp);
+  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
+
+}  // namespace pd
