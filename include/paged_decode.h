@@ -39,6 +39,10 @@ extern "C" {
 #define PD_ERR_UNSUPPORTED (-2)   /* valid request that no compiled kernel serves      */
 #define PD_ERR_WORKSPACE (-3)     /* workspace missing, misaligned or too small        */
 #define PD_ERR_CUDA (-4)          /* a CUDA runtime/driver call failed                 */
+#define PD_ERR_TOO_LARGE (-5)     /* needs more scratch than PD_STATIC_SCRATCH_BYTES   */
+
+/* Size of the library-owned scratch pd_decode_static works in. */
+#define PD_STATIC_SCRATCH_BYTES (8u << 20)
 
 /* kv_dtype: element type stored in k_cache / v_cache (pagedattn/config.py:16-31) */
 #define PD_KV_F16 0
@@ -187,6 +191,35 @@ PD_API int pd_merge(const PdMergeArgs* args);
 
 /* Dense dequantised fp16 gather (see PdGatherArgs). */
 PD_API int pd_gather(const PdGatherArgs* args);
+
+/*
+ * pd_decode for callers that have no scratch memory to give and may not allocate any.  It has
+ * no counterpart in the reference, whose launcher allocates its split scratch with
+ * torch.empty whenever the shape changes.
+ *
+ * Who needs it: a serving process that handed all free HBM to its KV-page pool at start-up, so
+ * a later cudaMalloc would fail; a plugin running on an engine's worker thread where the
+ * engine owns the allocator and forbids allocation on the decode path; a host with no
+ * allocator of its own at all (a thin C or FFI caller that only holds the pointers it was
+ * given).  Such callers pass q, out and the cache exactly as for pd_decode and leave
+ * `workspace` NULL (it is ignored); the streaming kernel's plan and partial-result slots live
+ * in a fixed PD_STATIC_SCRATCH_BYTES array compiled into the library, which every GPU that
+ * loads the library holds until the process exits.
+ *
+ * Limits and rules:
+ *   - only requests the streaming kernel serves (else PD_ERR_UNSUPPORTED), and only those whose
+ *     scratch need, pd_workspace_bytes() with kernel = PD_KERNEL_STREAM, is at most
+ *     PD_STATIC_SCRATCH_BYTES (else PD_ERR_TOO_LARGE; nothing is launched);
+ *   - the first call on each device looks up the array's device address; make that first call
+ *     before any stream capture begins;
+ *   - all calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to be cleared between calls (every word read is written first within
+ *     the call), but two calls whose kernels can overlap on the GPU (different streams, or
+ *     different host threads on different streams) race on it: keep calls on one stream or
+ *     order them yourself;
+ *   - no cudaMalloc, cudaFree or other allocating routine is called, host heap included.
+ */
+PD_API int pd_decode_static(const PdDecodeArgs* args);
 
 #ifdef __cplusplus
 }

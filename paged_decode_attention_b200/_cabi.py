@@ -72,7 +72,11 @@ class PdGatherArgs(ctypes.Structure):
 
 
 EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
-           "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather")
+           "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather",
+           "pd_decode_static")
+
+STATIC_SCRATCH_BYTES = 8 << 20
+ERR_TOO_LARGE = -5
 
 _lib = None
 
@@ -99,7 +103,7 @@ def load() -> ctypes.CDLL:
         raise NativeLibraryError(f"{LIB_PATH} has ABI {lib.pd_abi_version()}, expected {ABI_VERSION}")
     lib.pd_status_string.restype = ctypes.c_char_p
     lib.pd_status_string.argtypes = [ctypes.c_int]
-    for name in ("pd_decode", "pd_select_kernel"):
+    for name in ("pd_decode", "pd_select_kernel", "pd_decode_static"):
         getattr(lib, name).restype = ctypes.c_int
         getattr(lib, name).argtypes = [ctypes.POINTER(PdDecodeArgs)]
     lib.pd_decode_host.restype = ctypes.c_int

@@ -28,7 +28,7 @@ static bool aligned(const void* p, uintptr_t a) { return ((uintptr_t)p % a) == 0
 static int elem_bytes(int kv) { return (kv == PD_KV_F16 || kv == PD_KV_BF16) ? 2 : 1; }
 
 // Checks everything that can be checked without touching the device.
-static int validate(const PdDecodeArgs* a) {
+int validate(const PdDecodeArgs* a) {
   if (!a) return PD_ERR_INVALID_ARG;
   if (!a->q || !a->k_cache || !a->v_cache || !a->block_table || !a->seq_lens)
     return PD_ERR_INVALID_ARG;
@@ -64,7 +64,7 @@ static int validate(const PdDecodeArgs* a) {
   return PD_OK;
 }
 
-static void fill_params(const PdDecodeArgs* a, Params& p) {
+void fill_params(const PdDecodeArgs* a, Params& p) {
   p.q = a->q;
   p.out = a->out;
   p.q_sb = a->q_stride_b;
@@ -101,7 +101,7 @@ static void fill_params(const PdDecodeArgs* a, Params& p) {
   p.status = a->status;
 }
 
-static int resolve_sm_count(const PdDecodeArgs* a) {
+int resolve_sm_count(const PdDecodeArgs* a) {
   return a->sm_count > 0 ? a->sm_count : cached_sm_count();
 }
 
@@ -220,6 +220,7 @@ const char* pd_status_string(int status) {
     case PD_ERR_UNSUPPORTED: return "unsupported shape, dtype or stride";
     case PD_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case PD_ERR_CUDA: return "CUDA call failed";
+    case PD_ERR_TOO_LARGE: return "request needs more scratch than the library's fixed buffer holds";
     default: return "unknown status";
   }
 }

@@ -1010,4 +1010,130 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------------------------
+// pd_decode_static: the streaming decode with its scratch in library-owned device memory
+// ---------------------------------------------------------------------------------------------
+// Scratch of pd_decode_static.  It is part of the loaded module: every GPU that loads this
+// library holds these bytes from load until the process exits.  All calls share it.
+static __device__ __align__(256) unsigned char g_static_scratch[PD_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.  In host
+// code the array's name is only a handle for the runtime, not an address a kernel can use; the
+// address has to come from cudaGetSymbolAddress with the target device current.
+static void* static_scratch_address() {
+  static std::mutex mu;
+  static void* address[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    address[dev] = ptr;
+  }
+  return address[dev];
+}
+
+// Same tensor map as get_tensor_map builds, encoded straight into caller storage: no cache,
+// so nothing is allocated on the host either.
+static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  const int eb = k.kv == PD_KV_F16 ? 2 : 1;
+  const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
+  const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(out, eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+             const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
+  const Shape s = derive(a);
+  SmemPlan sm;
+  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
+  if (wl.total > (uint64_t)PD_STATIC_SCRATCH_BYTES) return PD_ERR_TOO_LARGE;
+  char* scratch = (char*)static_scratch_address();
+  if (!scratch) return PD_ERR_CUDA;
+
+  MapKey key{a->k_cache, a->kv_stride_block, a->kv_stride_token, a->kv_stride_head, a->head_dim,
+             a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
+  CUtensorMap mk, mv;
+  if (!encode_tensor_map_in_place(key, &mk)) return PD_ERR_CUDA;
+  key.base = a->v_cache;
+  if (!encode_tensor_map_in_place(key, &mv)) return PD_ERR_CUDA;
+
+  // Nothing in the scratch has to start at zero: the decode kernel writes the plan and every
+  // slot the plan names before the merge kernel, ordered after it on the stream, reads them.
+  StreamParams sp;
+  sp.p = p;
+  sp.p.num_splits = s.splits;
+  sp.p.part_lse = (float*)(scratch + wl.lse_off);
+  sp.p.part_o = (float*)(scratch + wl.o_off);
+  sp.nvseq = s.nvseq;
+  sp.nhb = s.nhb;
+  sp.splits = s.splits;
+  sp.nstage = sm.nstage;
+  sp.bar_off = sm.bar_off;
+  sp.meta_off = sm.meta_off;
+  sp.misc_off = sm.misc_off;
+  sp.prefix_off = sm.prefix_off;
+  sp.plan = (int32_t*)(scratch + wl.plan_off);
+  sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
+
+  const cudaStream_t st = (cudaStream_t)a->stream;
+  cudaError_t e;
+  if (a->kv_dtype == PD_KV_F16) {
+    e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else if (a->kv_dtype == PD_KV_E5M2) {
+    e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                 : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else {
+    e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  }
+  if (e != cudaSuccess) return PD_ERR_CUDA;
+
+  MergeSlotsParams mp;
+  mp.plan = sp.plan;
+  mp.part_o = sp.p.part_o;
+  mp.part_lse = sp.p.part_lse;
+  mp.batch = a->batch;
+  mp.hq = a->num_q_heads;
+  mp.group = a->num_q_heads / a->num_kv_heads;
+  mp.hb_heads = s.hb;
+  mp.splits = s.splits;
+  mp.d = a->head_dim;
+  mp.out = a->out;
+  mp.o_sb = a->out_stride_b;
+  mp.o_sh = a->out_stride_h;
+  mp.res_o = a->result_f32;
+  mp.res_lse = a->result_lse;
+  stream_merge_kernel<<<a->batch * a->num_q_heads, 128, 0, st>>>(mp);
+  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
+
 }  // namespace pd
+
+// Decode step for callers that cannot hand over scratch memory: see include/paged_decode.h.
+// The first call on a device looks up the scratch array's device address (one
+// cudaGetSymbolAddress with that device current); make that first call outside any stream
+// capture.  No cudaMalloc, cudaFree or other allocating routine is called, on any call.
+extern "C" PD_API int pd_decode_static(const PdDecodeArgs* args) {
+  using namespace pd;
+  const int rc = validate(args);
+  if (rc != PD_OK) return rc;
+  const int why = stream_supports(args);
+  if (why != PD_OK) return why;
+  const int sms = resolve_sm_count(args);
+  if (sms <= 0) return PD_ERR_CUDA;
+  Params p;
+  fill_params(args, p);
+  return stream_run_static(args, p, sms);
+}

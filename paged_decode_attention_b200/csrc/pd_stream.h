@@ -1,4 +1,5 @@
-// Host interface of the streaming decode kernel (pd_stream.cu) used by the C ABI layer.
+// Host interface between the C ABI layer (pd_api.cu) and the streaming decode kernel
+// (pd_stream.cu).
 #pragma once
 
 #include "pd_common.cuh"
@@ -14,5 +15,11 @@ uint64_t stream_workspace_bytes(const PdDecodeArgs* a, int sm_count);
 
 // Launches the streaming decode and its merge on a->stream.
 int stream_run(const PdDecodeArgs* a, Params& p, int sm_count);
+
+// Defined in pd_api.cu: argument checks that need no device, the device-side parameter block,
+// and the SM count of the current device (or the caller's override).
+int validate(const PdDecodeArgs* a);
+void fill_params(const PdDecodeArgs* a, Params& p);
+int resolve_sm_count(const PdDecodeArgs* a);
 
 }  // namespace pd

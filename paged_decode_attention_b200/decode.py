@@ -178,6 +178,31 @@ def paged_decode(
 paged_decode_triton = paged_decode
 
 
+def paged_decode_static(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor, *, block_n: int = 64,
+                        num_splits: int | None = None, sm_scale: float | None = None,
+                        status: torch.Tensor | None = None) -> torch.Tensor:
+    """``paged_decode`` without any allocation: for callers that may not allocate device memory.
+
+    Meant for code that runs where allocating is off limits — a process whose free HBM all
+    went to the KV-page pool, or a plugin on an engine thread that must not touch the
+    allocator.  ``out`` is therefore required (nothing is created here), and the kernel's
+    scratch is the fixed ``STATIC_SCRATCH_BYTES`` (8 MiB) array inside the library instead
+    of a torch buffer.  Requests the streaming kernel does not serve, or that need more
+    scratch than that, raise; calls that may overlap on the GPU must be ordered by the
+    caller because they share the array.  The first call on a device performs a one-time
+    address look-up and should happen before any stream capture.
+    """
+    if not q.is_cuda:
+        raise _cabi.NativeLibraryError("paged_decode_static runs on CUDA tensors only")
+    if out is None:
+        raise ValueError("paged_decode_static allocates nothing: pass `out`")
+    args = build_args(q, cache, out, block_n=block_n, num_splits=num_splits, sm_scale=sm_scale,
+                      kernel="stream", status=status)
+    with torch.cuda.device(q.device):
+        _cabi.check(_cabi.load().pd_decode_static(ctypes.byref(args)), "pd_decode_static")
+    return out
+
+
 def merge_partials(part_out: torch.Tensor, part_lse: torch.Tensor, out: torch.Tensor | None = None,
                    *, io_dtype: torch.dtype = torch.float16, want_f32: bool = False):
     """Merge ``P`` partial results by log-sum-exp on the GPU.
