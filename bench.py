@@ -212,7 +212,8 @@ def run_ours(args) -> None:
         step = runner.step
         launches_per_step = runner.launches_per_step
     else:
-        q, cache = synth.make(args.workload, device=dev, seed=args.seed + rank)
+        q, cache = synth.make(args.workload, device=dev, seed=args.seed + rank,
+                              batch=args.batch or None, seq_len=args.seq_len or None)
         out = torch.empty_like(q)
         dargs = pdec.build_args(q, cache, out, kernel=args.kernel,
                                 num_splits=args.num_splits if args.num_splits else None)
@@ -309,7 +310,7 @@ def run_ours(args) -> None:
         "data": "synthetic",
         "pct_of_8tbs": 100.0 * value / world / 8000.0,
         "config": {"workload": f"{args.workload}: {w.description}", "seed": args.seed,
-                   "kernel": args.kernel, "kv_bytes_per_gpu": my_bytes, "kv_bytes_job": job_bytes,
+                   "kernel": args.kernel, "batch": int(q.shape[0]), "kv_bytes_per_gpu": my_bytes, "kv_bytes_job": job_bytes,
                    "resident_pool_bytes_per_gpu": resident,
                    "l2": f"inputs ({resident / 1e6:.0f} MB per GPU) exceed the {L2_BYTES >> 20} MB L2"
                          if resident > 2 * L2_BYTES else "inputs fit in L2: latency-bound, no HBM claim",
@@ -346,6 +347,9 @@ def main() -> None:
     ap.add_argument("--kernel", choices=("auto", "simple", "stream"), default="auto")
     ap.add_argument("--num-splits", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0,
+                    help="shrink the workload to this many requests (profiling captures)")
+    ap.add_argument("--seq-len", type=int, default=0, help="force one length for every request")
     ap.add_argument("--cpu-tokens", type=int, default=40000,
                     help="size of the CPU sample in tokens")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -6,7 +6,8 @@
  * kernels.  It has no native interface to mirror, so this header defines the one a binding
  * for that entry point needs: plain pointers, sizes and element strides, an int status on
  * return, no exceptions, no torch types.  Every function is safe to call from several host
- * threads; the library owns no device memory and keeps no mutable state keyed by shapes.
+ * threads; the library owns no device memory apart from the fixed scratch of pd_decode_static
+ * and keeps no mutable state keyed by shapes.
  *
  * Conventions
  *   - all strides are in ELEMENTS of the tensor they describe, not bytes;
