@@ -219,9 +219,9 @@ def run_ours(args) -> None:
                                 num_splits=args.num_splits if args.num_splits else None)
         kernel_used = pdec.selected_kernel(dargs)
 
-        def step():
-            pda.paged_decode(q, cache, out=out, kernel=args.kernel,
-                             num_splits=args.num_splits if args.num_splits else None)
+        prepared = pda.DecodeStep(q, cache, out, kernel=args.kernel,
+                                  num_splits=args.num_splits if args.num_splits else None)
+        step = prepared.step
 
         launches_per_step = 2 if (kernel_used == "stream" or pdec.workspace_bytes(dargs) > 0) else 1
     my_bytes = cache.bytes_read_per_decode_step()
@@ -236,6 +236,30 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     sync_all()
+
+    # optional: the same steps replayed from a CUDA graph, to see GPU time without host launch gaps
+    graph_us = None
+    if args.graph_steps > 0 and not kv_sharded:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.graph_steps):
+                step()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(1, args.steps // args.graph_steps)
+        g0.record()
+        for _ in range(reps):
+            graph.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        graph_us = g0.elapsed_time(g1) * 1e3 / (reps * args.graph_steps)
 
     # ---- device-timed region: K steps, CUDA events on the launching stream -------------
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -323,7 +347,10 @@ def run_ours(args) -> None:
         "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
+        "api": "DecodeStep.step (paged_decode prepared once; same C-ABI call pd_decode)",
     }
+    if graph_us is not None:
+        line["us_per_call_cuda_graph"] = graph_us
     if world == 1 and not args.no_cpu:
         r = cpu_port_timing(cache, q, steps=2, warmup=1, budget_tokens=args.cpu_tokens)
         line["cpu_baseline"] = {"value": r["bytes"] / r["torch_s"] / 1e9, "unit": "GB/s",
@@ -353,6 +380,8 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=40000,
                     help="size of the CPU sample in tokens")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--graph-steps", type=int, default=0,
+                    help="also time this many steps per CUDA-graph replay (GPU time without host gaps)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

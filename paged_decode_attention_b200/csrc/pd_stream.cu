@@ -260,6 +260,202 @@ __device__ __forceinline__ int find_vseq(const int* prefix, int n, int g) {
   return lo;
 }
 
+// int8 pair -> f16x2 holding 1152 + x (w is x ^ 0x80 per byte): one prmt, no subtraction.
+__device__ __forceinline__ uint32_t cvt_pair_biased(uint32_t w, bool upper) {
+  return __byte_perm(w, 0x64646464u, upper ? 0x4342u : 0x4140u);
+}
+
+// One 16-token tile of one kv head for one consumer warp: S = Q K^T, base-2 online softmax,
+// O += P V.  `kbase` is the warp's K rows in the stage (V follows at TILE_BYTES), `scales` the
+// address of this head's K scale of token 0 (V scales 1024 bytes further, token pitch hkv * 2).
+// MASKED tiles hold fewer than 16 live tokens (`valid`); full tiles skip every mask.
+template <int KV, int D, int HB, bool SCALED, bool MASKED>
+__device__ __forceinline__ void consume_tile(
+    const uint32_t kbase, const uint32_t scales, const int hkv, const int valid,
+    const float scale_log2, const int lane,
+    const uint32_t (&qa)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][4], const float qbias0,
+    const float qbias1, float& m0, float& m1, float& l0, float& l1,
+    float (&o)[StreamCfg<KV, D, HB, SCALED>::NT][4]) {
+  using C = StreamCfg<KV, D, HB, SCALED>;
+  constexpr unsigned kFull = 0xffffffffu;
+  const int gq = lane >> 2, tq = lane & 3;
+  const uint32_t vbase = kbase + C::TILE_BYTES;
+
+  // ---- S = Q K^T: two 8-token n-tiles -----------------------------------------------------
+  float s[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+  if constexpr (KV == PD_KV_F16) {
+    // lane l addresses row (token) of 8x8 matrix l/8: matrices (nt0, lo), (nt0, hi), (nt1, lo),
+    // (nt1, hi) where lo/hi are the two 16-byte chunks of the k-step
+    const int mi = lane >> 3;
+    const int token = 8 * (mi >> 1) + (lane & 7);
+    const uint32_t row = kbase + token * 128;
+#pragma unroll
+    for (int ks = 0; ks < C::KSTEPS; ++ks) {
+      const int chunk = ((2 * ks) & 7) + (mi & 1);
+      uint32_t b[4];
+      ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
+      mma_f16(s[0], qa[ks], b[0], b[1]);
+      mma_f16(s[1], qa[ks], b[2], b[3]);
+    }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int token = 8 * nt + gq;
+      const uint32_t row = kbase + token * 128;
+#pragma unroll
+      for (int jh = 0; jh < 2; ++jh) {
+        uint32_t wv[4];
+        lds128(row + (((2 * tq + jh) ^ (token & 7)) << 4), wv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if constexpr (KV == PD_KV_I8) {
+            const uint32_t x = wv[i] ^ 0x80808080u;
+            mma_f16(s[nt], qa[4 * jh + i], cvt_pair_biased(x, false), cvt_pair_biased(x, true));
+          } else {
+            mma_f16(s[nt], qa[4 * jh + i], cvt_pair<KV>(wv[i], false), cvt_pair<KV>(wv[i], true));
+          }
+        }
+      }
+    }
+  }
+
+  // ---- scale, mask, online softmax ----------------------------------------------------------
+  float vsc[2][2];  // V scale (times 256) of the thread's four tokens
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int token = 8 * nt + 2 * tq + e;
+      float f = scale_log2;
+      vsc[nt][e] = 1.f;
+      if constexpr (SCALED) {
+        const uint32_t sa = scales + token * hkv * 2;
+        f *= lds_half(sa);
+        vsc[nt][e] = lds_half(sa + 1024) * 256.f;
+      }
+      float x0 = s[nt][e], x1 = s[nt][2 + e];
+      if constexpr (KV == PD_KV_I8) {
+        x0 -= qbias0;
+        x1 -= qbias1;
+      }
+      x0 *= f;
+      x1 *= f;
+      if constexpr (MASKED) {
+        const bool live = token < valid;
+        x0 = live ? x0 : -INFINITY;
+        x1 = live ? x1 : -INFINITY;
+      }
+      s[nt][e] = x0;
+      s[nt][2 + e] = x1;
+    }
+  }
+  float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+  float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 2));
+  const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: token 0 is live
+  const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+  m0 = mn0;
+  m1 = mn1;
+  float ps0 = 0.f, ps1 = 0.f;
+  uint32_t pa[4];
+  {
+    float pr[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float x0 = fast_exp2(s[nt][e] - mn0);
+        const float x1 = fast_exp2(s[nt][2 + e] - mn1);
+        ps0 += x0;
+        ps1 += x1;
+        pr[nt][e] = SCALED ? x0 * vsc[nt][e] : x0;
+        pr[nt][2 + e] = SCALED ? x1 * vsc[nt][e] : x1;
+      }
+    }
+    pa[0] = pack_half2(pr[0][0], pr[0][1]);  // row gq,     tokens 2tq, 2tq+1
+    pa[1] = pack_half2(pr[0][2], pr[0][3]);  // row gq + 8
+    pa[2] = pack_half2(pr[1][0], pr[1][1]);  // row gq,     tokens 2tq+8, 2tq+9
+    pa[3] = pack_half2(pr[1][2], pr[1][3]);
+  }
+  l0 = l0 * a0 + ps0;
+  l1 = l1 * a1 + ps1;
+  // the running maxima settle after the first tiles; skip the rescale when nobody's moved
+  if (__any_sync(kFull, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+    for (int n = 0; n < C::NT; ++n) {
+      o[n][0] *= a0;
+      o[n][1] *= a0;
+      o[n][2] *= a1;
+      o[n][3] *= a1;
+    }
+  }
+
+  // ---- O += P V ---------------------------------------------------------------------------------
+  // Rows of V past `valid` hold whatever the page holds.  Every int8 byte is a finite number,
+  // so P = 0 already removes it; f16 / e5m2 garbage may be NaN and is zeroed in masked tiles.
+  constexpr bool kMaskV = MASKED && KV != PD_KV_I8;
+  uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2tq, 2tq+1), (2tq+8, 2tq+9)
+  if constexpr (kMaskV) {
+    keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
+    keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
+  }
+  if constexpr (KV == PD_KV_F16) {
+    // transposed 8x8 matrices: (tokens 0-7, chunk nd), (8-15, nd), (0-7, nd+1), (8-15, nd+1)
+    const int mi = lane >> 3;
+    const int token = 8 * (mi & 1) + (lane & 7);
+    const uint32_t row = vbase + token * 128;
+#pragma unroll
+    for (int nd = 0; nd < C::NT; nd += 2) {
+      const int chunk = (nd & 7) + (mi >> 1);
+      uint32_t b[4];
+      ldmatrix_x4_trans(row + (nd >> 3) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
+      if constexpr (kMaskV) {
+        b[0] &= keep_lo;
+        b[1] &= keep_hi;
+        b[2] &= keep_lo;
+        b[3] &= keep_hi;
+      }
+      mma_f16(o[nd], pa, b[0], b[1]);
+      mma_f16(o[nd + 1], pa, b[2], b[3]);
+    }
+  } else {
+    // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of columns
+    // 4*(gq + 8*jj) .. +3 and transposes bytes in registers.  Output n-tile 4*jj + i then holds
+    // head_dim column 32*jj + 4*c + i for fragment column c; the epilogue undoes it.
+    const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
+#pragma unroll
+    for (int jj = 0; jj < D / 32; ++jj) {
+      uint32_t r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int chunk = 2 * jj + (gq >> 2);
+        r[k] = lds32(vbase + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) + ((gq & 3) << 2));
+        if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
+      }
+      // bytes (c0, c2) and (c1, c3) of the token pairs side by side
+      const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
+      const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
+      uint32_t b[4][2] = {{cvt_pair<KV>(e01, false), cvt_pair<KV>(e23, false)},
+                          {cvt_pair<KV>(o01, false), cvt_pair<KV>(o23, false)},
+                          {cvt_pair<KV>(e01, true), cvt_pair<KV>(e23, true)},
+                          {cvt_pair<KV>(o01, true), cvt_pair<KV>(o23, true)}};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if constexpr (kMaskV) {
+          b[i][0] &= keep_lo;
+          b[i][1] &= keep_hi;
+        }
+        mma_f16(o[4 * jj + i], pa, b[i][0], b[i][1]);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
@@ -337,6 +533,8 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
     }
     for (int v = tid; v <= nv; v += C::THREADS) sp.plan[2 + v] = prefix[v];
   }
+  // let the merge kernel's launch overlap this grid (it waits for this grid to finish)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (g0 >= g1) return;  // nothing for this worker (no barrier is used after this point)
 
   // =============================== producer warp =============================================
@@ -460,6 +658,27 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
       }
     }
 
+    // int8 keys are fed to the tensor core as 1152 + x (see cvt_pair_biased); the surplus
+    // 1152 * sum_d q[row][d] is removed from the scores afterwards
+    float qbias0 = 0.f, qbias1 = 0.f;
+    if constexpr (KV == PD_KV_I8) {
+#pragma unroll
+      for (int ks = 0; ks < C::KSTEPS; ++ks) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][0]));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][1]));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][2]));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][3]));
+        qbias0 += (a.x + a.y) + (c.x + c.y);
+        qbias1 += (b.x + b.y) + (d.x + d.y);
+      }
+      qbias0 += __shfl_xor_sync(kFull, qbias0, 1);
+      qbias0 += __shfl_xor_sync(kFull, qbias0, 2);
+      qbias1 += __shfl_xor_sync(kFull, qbias1, 1);
+      qbias1 += __shfl_xor_sync(kFull, qbias1, 2);
+      qbias0 *= 1152.f;
+      qbias1 *= 1152.f;
+    }
+
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     float o[C::NT][4];
 #pragma unroll
@@ -472,151 +691,16 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         break;
       }
       if (meta[st] == 0) {
-        const uint32_t kbase = stage0 + (uint32_t)st * C::STAGE_BYTES + role * (kTileTokens * 128);
-        const uint32_t vbase = kbase + C::TILE_BYTES;
+        const uint32_t sbase = stage0 + (uint32_t)st * C::STAGE_BYTES;
+        const uint32_t kbase = sbase + role * (kTileTokens * 128);
+        const uint32_t scales = sbase + 2 * C::TILE_BYTES + kvh * 2;
         const int remaining = vi.hi - (vi.lo + j * kTileTokens);
-        const int valid = remaining < kTileTokens ? remaining : kTileTokens;
-
-        // ---- S = Q K^T: two 8-token n-tiles ---------------------------------------------
-        float s[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-        if constexpr (KV == PD_KV_F16) {
-          // lane l addresses row (token) of 8x8 matrix l/8: matrices (nt0, lo), (nt0, hi),
-          // (nt1, lo), (nt1, hi) where lo/hi are the two 16-byte chunks of the k-step
-          const int mi = lane >> 3;
-          const int token = 8 * (mi >> 1) + (lane & 7);
-          const uint32_t row = kbase + token * 128;
-#pragma unroll
-          for (int ks = 0; ks < C::KSTEPS; ++ks) {
-            const int chunk = ((2 * ks) & 7) + (mi & 1);
-            uint32_t b[4];
-            ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
-            mma_f16(s[0], qa[ks], b[0], b[1]);
-            mma_f16(s[1], qa[ks], b[2], b[3]);
-          }
-        } else {
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            const int token = 8 * nt + gq;
-            const uint32_t row = kbase + token * 128;
-#pragma unroll
-            for (int jh = 0; jh < 2; ++jh) {
-              uint32_t wv[4];
-              lds128(row + (((2 * tq + jh) ^ (token & 7)) << 4), wv);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const uint32_t x = KV == PD_KV_I8 ? wv[i] ^ 0x80808080u : wv[i];
-                mma_f16(s[nt], qa[4 * jh + i], cvt_pair<KV>(x, false), cvt_pair<KV>(x, true));
-              }
-            }
-          }
-        }
-
-        // ---- scale, mask, online softmax ------------------------------------------------
-        float vsc[2][2];  // V scale of the thread's four tokens
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int token = 8 * nt + 2 * tq + e;
-            float f = p.scale_log2;
-            vsc[nt][e] = 1.f;
-            if constexpr (SCALED) {
-              const uint32_t sa = stage0 + (uint32_t)st * C::STAGE_BYTES + 2 * C::TILE_BYTES +
-                                  (token * p.hkv + kvh) * 2;
-              f *= lds_half(sa);
-              vsc[nt][e] = lds_half(sa + 1024) * 256.f;
-            }
-            const bool live = token < valid;
-            s[nt][e] = live ? s[nt][e] * f : -INFINITY;
-            s[nt][2 + e] = live ? s[nt][2 + e] * f : -INFINITY;
-          }
-        }
-        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: token 0 is live
-        const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
-        m0 = mn0;
-        m1 = mn1;
-        float ps0 = 0.f, ps1 = 0.f;
-        uint32_t pa[4];
-        {
-          float pr[2][4];
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float x0 = fast_exp2(s[nt][e] - mn0);
-              const float x1 = fast_exp2(s[nt][2 + e] - mn1);
-              ps0 += x0;
-              ps1 += x1;
-              pr[nt][e] = x0 * vsc[nt][e];
-              pr[nt][2 + e] = x1 * vsc[nt][e];
-            }
-          }
-          pa[0] = pack_half2(pr[0][0], pr[0][1]);  // row gq,     tokens 2tq, 2tq+1
-          pa[1] = pack_half2(pr[0][2], pr[0][3]);  // row gq + 8
-          pa[2] = pack_half2(pr[1][0], pr[1][1]);  // row gq,     tokens 2tq+8, 2tq+9
-          pa[3] = pack_half2(pr[1][2], pr[1][3]);
-        }
-        l0 = l0 * a0 + ps0;
-        l1 = l1 * a1 + ps1;
-#pragma unroll
-        for (int n = 0; n < C::NT; ++n) {
-          o[n][0] *= a0;
-          o[n][1] *= a0;
-          o[n][2] *= a1;
-          o[n][3] *= a1;
-        }
-
-        // ---- O += P V -----------------------------------------------------------------------
-        // rows of V past `valid` hold whatever the page holds: zero them so 0 * NaN cannot occur
-        uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2tq,2tq+1), (+8,+9)
-        if (valid < kTileTokens) {
-          keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
-          keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
-        }
-        if constexpr (KV == PD_KV_F16) {
-          // transposed 8x8 matrices: (tokens 0-7, chunk nd), (8-15, nd), (0-7, nd+1), (8-15, nd+1)
-          const int mi = lane >> 3;
-          const int token = 8 * (mi & 1) + (lane & 7);
-          const uint32_t row = vbase + token * 128;
-#pragma unroll
-          for (int nd = 0; nd < C::NT; nd += 2) {
-            const int chunk = (nd & 7) + (mi >> 1);
-            uint32_t b[4];
-            ldmatrix_x4_trans(row + (nd >> 3) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
-            mma_f16(o[nd], pa, b[0] & keep_lo, b[1] & keep_hi);
-            mma_f16(o[nd + 1], pa, b[2] & keep_lo, b[3] & keep_hi);
-          }
-        } else {
-          // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of columns
-          // 4*(gq + 8*jj) .. +3 and transposes bytes in registers.  Output n-tile 4*jj + i then
-          // holds head_dim column 32*jj + 4*c + i for fragment column c; the epilogue undoes it.
-          const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
-#pragma unroll
-          for (int jj = 0; jj < D / 32; ++jj) {
-            uint32_t r[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int chunk = 2 * jj + (gq >> 2);
-              r[k] = lds32(vbase + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) + ((gq & 3) << 2));
-              if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
-            }
-            // bytes (c0, c2) and (c1, c3) of the token pairs side by side
-            const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
-            const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
-            mma_f16(o[4 * jj + 0], pa, cvt_pair<KV>(e01, false) & keep_lo, cvt_pair<KV>(e23, false) & keep_hi);
-            mma_f16(o[4 * jj + 1], pa, cvt_pair<KV>(o01, false) & keep_lo, cvt_pair<KV>(o23, false) & keep_hi);
-            mma_f16(o[4 * jj + 2], pa, cvt_pair<KV>(e01, true) & keep_lo, cvt_pair<KV>(e23, true) & keep_hi);
-            mma_f16(o[4 * jj + 3], pa, cvt_pair<KV>(o01, true) & keep_lo, cvt_pair<KV>(o23, true) & keep_hi);
-          }
-        }
+        if (remaining >= kTileTokens)
+          consume_tile<KV, D, HB, SCALED, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2, lane,
+                                                 qa, qbias0, qbias1, m0, m1, l0, l1, o);
+        else
+          consume_tile<KV, D, HB, SCALED, true>(kbase, scales, p.hkv, remaining, p.scale_log2, lane, qa,
+                                                qbias0, qbias1, m0, m1, l0, l1, o);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * st);
@@ -693,6 +777,9 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
 // a single unsplit segment covered were written by the decode kernel and are left alone; rows
 // with no tokens become zero.
 __global__ void __launch_bounds__(128) stream_merge_kernel(const MergeSlotsParams mp) {
+  // Launched with programmatic stream serialization: the CTAs may become resident while the
+  // decode grid still runs; nothing of its output is touched before this wait returns.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int row = blockIdx.x;
   const int b = row / mp.hq, hq = row % mp.hq;
   const int kvh = hq / mp.group;
@@ -948,6 +1035,22 @@ static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& 
   }
 }
 
+// Launches the slot merge behind the decode kernel with programmatic dependent launch, so its
+// launch latency overlaps the decode grid's tail.
+static cudaError_t launch_slot_merge(const MergeSlotsParams& mp, int rows, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)rows);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, stream_merge_kernel, mp);
+}
+
 int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   const Shape s = derive(a);
   SmemPlan sm;
@@ -1006,8 +1109,7 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   mp.o_sh = a->out_stride_h;
   mp.res_o = a->result_f32;
   mp.res_lse = a->result_lse;
-  stream_merge_kernel<<<a->batch * a->num_q_heads, 128, 0, st>>>(mp);
-  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+  return launch_slot_merge(mp, a->batch * a->num_q_heads, st) == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1115,8 +1217,7 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   mp.o_sh = a->out_stride_h;
   mp.res_o = a->result_f32;
   mp.res_lse = a->result_lse;
-  stream_merge_kernel<<<a->batch * a->num_q_heads, 128, 0, st>>>(mp);
-  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+  return launch_slot_merge(mp, a->batch * a->num_q_heads, st) == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
 }  // namespace pd

@@ -50,17 +50,28 @@ def pick_num_splits(batch: int, num_kv_heads: int, max_seq_len: int, sm_count: i
                                                int(sm_count), int(block_n)))
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+def _workspace(device: torch.device, nbytes: int, stream: int | None = None) -> torch.Tensor | None:
     if nbytes == 0:
         return None
-    key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
-    with _ws_lock:
-        buf = _ws_cache.get(key)
-        if buf is None or buf.numel() < nbytes:
-            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-            _ws_cache[key] = buf
+    if stream is None:
+        stream = torch.cuda.current_stream(device).cuda_stream
+    key = (device.index, stream)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        with _ws_lock:
+            buf = _ws_cache.get(key)
+            if buf is None or buf.numel() < nbytes:
+                buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+                _ws_cache[key] = buf
     return buf
+
+
+def _call_on_device(device: torch.device, fn, *fn_args) -> int:
+    """Runs a native entry point with `device` current (switching only when it is not)."""
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return fn(*fn_args)
+    with torch.cuda.device(device):
+        return fn(*fn_args)
 
 
 def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *, block_n: int = 64,
@@ -165,13 +176,62 @@ def paged_decode(
     args = build_args(q, cache, out, block_n=block_n, num_splits=num_splits, sm_scale=sm_scale,
                       kernel=kernel, result_f32=result_f32, result_lse=result_lse, status=status,
                       max_seq_len=max_seq_len)
-    with torch.cuda.device(q.device):
-        ws = _workspace(q.device, workspace_bytes(args))
-        if ws is not None:
-            args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
-        _cabi.check(_cabi.load().pd_decode(ctypes.byref(args)), "pd_decode")
-    STATS["decode_launches"] += 1
+    _launch(q.device, args)
     return out
+
+
+def _launch(device: torch.device, args: _cabi.PdDecodeArgs) -> None:
+    lib = _cabi.load()
+    need = ctypes.c_uint64(0)
+    rc = _call_on_device(device, lib.pd_workspace_bytes, ctypes.byref(args), ctypes.byref(need))
+    if rc != 0:
+        _cabi.check(rc, "pd_workspace_bytes")
+    ws = _workspace(device, int(need.value), args.stream)
+    if ws is not None:
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    rc = _call_on_device(device, lib.pd_decode, ctypes.byref(args))
+    if rc != 0:
+        _cabi.check(rc, "pd_decode")
+    STATS["decode_launches"] += 1
+
+
+class DecodeStep:
+    """A decode call prepared once and replayed: for loops that decode into the same buffers.
+
+    ``paged_decode`` re-reads every pointer, stride and size on each call.  When q, out and
+    the cache tensors stay where they are between steps (a serving loop that updates the
+    block table and lengths in place), that work can be done once: ``DecodeStep(q, cache,
+    out)`` validates and fills the argument block and attaches the scratch, ``step()`` only
+    refreshes the stream and crosses the C ABI.  Results are those of ``paged_decode``.
+    """
+
+    def __init__(self, q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None = None, **kw):
+        if not q.is_cuda:
+            raise _cabi.NativeLibraryError("DecodeStep runs on CUDA tensors only; there is no CPU path")
+        self.out = torch.empty_like(q) if out is None else out
+        self.device = q.device
+        self._keep = (q, cache, self.out, kw.get("result_f32"), kw.get("result_lse"), kw.get("status"))
+        self.args = build_args(q, cache, self.out, **kw)
+        need = ctypes.c_uint64(0)
+        _cabi.check(_call_on_device(self.device, _cabi.load().pd_workspace_bytes, ctypes.byref(self.args),
+                                    ctypes.byref(need)), "pd_workspace_bytes")
+        # private scratch: the step may be replayed on any stream
+        self._ws = (torch.empty(int(need.value), dtype=torch.uint8, device=self.device)
+                    if need.value else None)
+        if self._ws is not None:
+            self.args.workspace, self.args.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
+        self._fn = _cabi.load().pd_decode
+        self._ref = ctypes.byref(self.args)
+
+    def step(self) -> torch.Tensor:
+        self.args.stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = _call_on_device(self.device, self._fn, self._ref)
+        if rc != 0:
+            _cabi.check(rc, "pd_decode")
+        STATS["decode_launches"] += 1
+        return self.out
+
+    __call__ = step
 
 
 # Drop-in name of the reference's entry point (pagedattn/triton_decode.py:285).
@@ -198,8 +258,8 @@ def paged_decode_static(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor,
         raise ValueError("paged_decode_static allocates nothing: pass `out`")
     args = build_args(q, cache, out, block_n=block_n, num_splits=num_splits, sm_scale=sm_scale,
                       kernel="stream", status=status)
-    with torch.cuda.device(q.device):
-        _cabi.check(_cabi.load().pd_decode_static(ctypes.byref(args)), "pd_decode_static")
+    _cabi.check(_call_on_device(q.device, _cabi.load().pd_decode_static, ctypes.byref(args)),
+                "pd_decode_static")
     return out
 
 
@@ -257,8 +317,10 @@ class HostDecoder:
         self.out_dev = torch.empty_like(self.q_dev)
         self.cache = cache
         self.args = build_args(self.q_dev, cache, self.out_dev, sm_scale=sm_scale, kernel=kernel)
-        with torch.cuda.device(dev):
-            self.ws = _workspace(dev, workspace_bytes(self.args))
+        need = ctypes.c_uint64(0)
+        _cabi.check(_call_on_device(dev, _cabi.load().pd_workspace_bytes, ctypes.byref(self.args),
+                                    ctypes.byref(need)), "pd_workspace_bytes")
+        self.ws = torch.empty(int(need.value), dtype=torch.uint8, device=dev) if need.value else None
         if self.ws is not None:
             self.args.workspace, self.args.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
         self.h2d_bytes = (self.q_dev.numel() * 2 + cache.block_table.numel() * 4 + cache.seq_lens.numel() * 4)
@@ -273,7 +335,7 @@ class HostDecoder:
                             out_host.data_ptr())
         dev = self.q_dev.device
         self.args.stream = torch.cuda.current_stream(dev).cuda_stream
-        with torch.cuda.device(dev):
-            _cabi.check(_cabi.load().pd_decode_host(ctypes.byref(self.args), ctypes.byref(io)),
-                        "pd_decode_host")
+        rc = _call_on_device(dev, _cabi.load().pd_decode_host, ctypes.byref(self.args), ctypes.byref(io))
+        if rc != 0:
+            _cabi.check(rc, "pd_decode_host")
         return out_host
