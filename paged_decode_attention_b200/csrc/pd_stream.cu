@@ -64,7 +64,7 @@ struct StreamCfg {
   static constexpr int SCALE_BYTES = SCALED ? 2048 : 0;      // K scales at +0, V scales at +1024
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES + SCALE_BYTES;
   static constexpr int KSTEPS = D / 16;
-  static constexpr int NT = D / 8;                           // output n-tiles
+  static constexpr int MT = D / 16;                          // 16-row tiles of head_dim in O^T
 };
 
 struct StreamParams {
@@ -264,169 +264,181 @@ __device__ __forceinline__ int find_vseq(const int* prefix, int n, int g) {
 __device__ __forceinline__ uint32_t cvt_pair_biased(uint32_t w, bool upper) {
   return __byte_perm(w, 0x64646464u, upper ? 0x4342u : 0x4140u);
 }
+// Transposes an 8x8 matrix of 16-bit elements held one row-pair per thread (ldmatrix layout).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
 
-// One 16-token tile of one kv head for one consumer warp: S = Q K^T, base-2 online softmax,
-// O += P V.  `kbase` is the warp's K rows in the stage (V follows at TILE_BYTES), `scales` the
-// address of this head's K scale of token 0 (V scales 1024 bytes further, token pitch hkv * 2).
+// One 16-token tile of one kv head for one consumer warp.  The products are taken with the
+// tokens on the M axis of the mma and the query heads of the group on its N axis ("swapped"):
+//   S^T[16 tokens x 8 heads] = K[16 x D] * Q^T,   O^T[D x 8 heads] += V^T[D x 16] * P^T
+// so a group of up to 8 heads fills the 8-wide N dimension instead of padding a 16-row M
+// (NG = 2 covers groups of 9..16).  Thread (g = lane / 4, t = lane % 4) owns tokens g and g + 8
+// of S^T and heads 2t, 2t + 1 (+ 8 per n-tile), the same heads it owns in O^T, so the softmax
+// state (m, l) stays in the thread; P^T reaches the B-operand layout with two movmatrix.
+// `kbase` is the warp's K rows in the stage (V follows at TILE_BYTES), `scales` the address of
+// this head's K scale of token 0 (V scales 1024 bytes further, token pitch hkv * 2).
 // MASKED tiles hold fewer than 16 live tokens (`valid`); full tiles skip every mask.
-template <int KV, int D, int HB, bool SCALED, bool MASKED>
+template <int KV, int D, int HB, bool SCALED, int NG, bool MASKED>
 __device__ __forceinline__ void consume_tile(
     const uint32_t kbase, const uint32_t scales, const int hkv, const int valid,
     const float scale_log2, const int lane,
-    const uint32_t (&qa)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][4], const float qbias0,
-    const float qbias1, float& m0, float& m1, float& l0, float& l1,
-    float (&o)[StreamCfg<KV, D, HB, SCALED>::NT][4]) {
+    const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qbias)[NG][2],
+    float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4]) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
   const int gq = lane >> 2, tq = lane & 3;
   const uint32_t vbase = kbase + C::TILE_BYTES;
 
-  // ---- S = Q K^T: two 8-token n-tiles -----------------------------------------------------
-  float s[2][4];
+  // ---- S^T = K Q^T ------------------------------------------------------------------------------
+  float s[NG][4];
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+  for (int ng = 0; ng < NG; ++ng) s[ng][0] = s[ng][1] = s[ng][2] = s[ng][3] = 0.f;
   if constexpr (KV == PD_KV_F16) {
-    // lane l addresses row (token) of 8x8 matrix l/8: matrices (nt0, lo), (nt0, hi), (nt1, lo),
-    // (nt1, hi) where lo/hi are the two 16-byte chunks of the k-step
+    // A fragments by ldmatrix: matrices (tokens 0-7, lo), (8-15, lo), (0-7, hi), (8-15, hi) where
+    // lo/hi are the two 16-byte chunks of the k-step
     const int mi = lane >> 3;
-    const int token = 8 * (mi >> 1) + (lane & 7);
+    const int token = 8 * (mi & 1) + (lane & 7);
     const uint32_t row = kbase + token * 128;
 #pragma unroll
     for (int ks = 0; ks < C::KSTEPS; ++ks) {
-      const int chunk = ((2 * ks) & 7) + (mi & 1);
-      uint32_t b[4];
-      ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
-      mma_f16(s[0], qa[ks], b[0], b[1]);
-      mma_f16(s[1], qa[ks], b[2], b[3]);
+      const int chunk = ((2 * ks) & 7) + (mi >> 1);
+      uint32_t a[4];
+      ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) mma_f16(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
     }
   } else {
+    // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each row give
+    // eight words, word i of chunk jh feeding k-step 4*jh + i
+    const uint32_t row0 = kbase + gq * 128, row1 = row0 + 8 * 128;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int token = 8 * nt + gq;
-      const uint32_t row = kbase + token * 128;
+    for (int jh = 0; jh < 2; ++jh) {
+      const uint32_t ch = (uint32_t)((2 * tq + jh) ^ (gq & 7)) << 4;
+      uint32_t w0[4], w1[4];
+      lds128(row0 + ch, w0);
+      lds128(row1 + ch, w1);
 #pragma unroll
-      for (int jh = 0; jh < 2; ++jh) {
-        uint32_t wv[4];
-        lds128(row + (((2 * tq + jh) ^ (token & 7)) << 4), wv);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          if constexpr (KV == PD_KV_I8) {
-            const uint32_t x = wv[i] ^ 0x80808080u;
-            mma_f16(s[nt], qa[4 * jh + i], cvt_pair_biased(x, false), cvt_pair_biased(x, true));
-          } else {
-            mma_f16(s[nt], qa[4 * jh + i], cvt_pair<KV>(wv[i], false), cvt_pair<KV>(wv[i], true));
-          }
+      for (int i = 0; i < 4; ++i) {
+        uint32_t a[4];
+        if constexpr (KV == PD_KV_I8) {
+          const uint32_t x0 = w0[i] ^ 0x80808080u, x1 = w1[i] ^ 0x80808080u;
+          a[0] = cvt_pair_biased(x0, false);
+          a[1] = cvt_pair_biased(x1, false);
+          a[2] = cvt_pair_biased(x0, true);
+          a[3] = cvt_pair_biased(x1, true);
+        } else {
+          a[0] = cvt_pair<KV>(w0[i], false);
+          a[1] = cvt_pair<KV>(w1[i], false);
+          a[2] = cvt_pair<KV>(w0[i], true);
+          a[3] = cvt_pair<KV>(w1[i], true);
         }
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng) mma_f16(s[ng], a, qb[4 * jh + i][ng][0], qb[4 * jh + i][ng][1]);
       }
     }
   }
 
-  // ---- scale, mask, online softmax ----------------------------------------------------------
-  float vsc[2][2];  // V scale (times 256) of the thread's four tokens
-#pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int token = 8 * nt + 2 * tq + e;
-      float f = scale_log2;
-      vsc[nt][e] = 1.f;
-      if constexpr (SCALED) {
-        const uint32_t sa = scales + token * hkv * 2;
-        f *= lds_half(sa);
-        vsc[nt][e] = lds_half(sa + 1024) * 256.f;
-      }
-      float x0 = s[nt][e], x1 = s[nt][2 + e];
-      if constexpr (KV == PD_KV_I8) {
-        x0 -= qbias0;
-        x1 -= qbias1;
-      }
-      x0 *= f;
-      x1 *= f;
-      if constexpr (MASKED) {
-        const bool live = token < valid;
-        x0 = live ? x0 : -INFINITY;
-        x1 = live ? x1 : -INFINITY;
-      }
-      s[nt][e] = x0;
-      s[nt][2 + e] = x1;
-    }
+  // ---- scale, mask, online softmax; P^T into B-operand layout ---------------------------------
+  float f0 = scale_log2, f1 = scale_log2;  // tokens g and g + 8
+  float vs0 = 1.f, vs1 = 1.f;              // their V scales (times 256)
+  if constexpr (SCALED) {
+    const uint32_t sa = scales + gq * hkv * 2;
+    f0 *= lds_half(sa);
+    f1 *= lds_half(sa + 8 * hkv * 2);
+    vs0 = lds_half(sa + 1024) * 256.f;
+    vs1 = lds_half(sa + 1024 + 8 * hkv * 2) * 256.f;
   }
-  float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-  float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 1));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 2));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 1));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 2));
-  const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: token 0 is live
-  const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
-  m0 = mn0;
-  m1 = mn1;
-  float ps0 = 0.f, ps1 = 0.f;
-  uint32_t pa[4];
-  {
-    float pr[2][4];
+  uint32_t pb[NG][2];
+  float alpha[NG][2];
+  bool moved = false;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float x0 = fast_exp2(s[nt][e] - mn0);
-        const float x1 = fast_exp2(s[nt][2 + e] - mn1);
-        ps0 += x0;
-        ps1 += x1;
-        pr[nt][e] = SCALED ? x0 * vsc[nt][e] : x0;
-        pr[nt][2 + e] = SCALED ? x1 * vsc[nt][e] : x1;
-      }
+  for (int ng = 0; ng < NG; ++ng) {
+    float x0 = s[ng][0], x1 = s[ng][1], x2 = s[ng][2], x3 = s[ng][3];
+    if constexpr (KV == PD_KV_I8) {
+      x0 -= qbias[ng][0];
+      x1 -= qbias[ng][1];
+      x2 -= qbias[ng][0];
+      x3 -= qbias[ng][1];
     }
-    pa[0] = pack_half2(pr[0][0], pr[0][1]);  // row gq,     tokens 2tq, 2tq+1
-    pa[1] = pack_half2(pr[0][2], pr[0][3]);  // row gq + 8
-    pa[2] = pack_half2(pr[1][0], pr[1][1]);  // row gq,     tokens 2tq+8, 2tq+9
-    pa[3] = pack_half2(pr[1][2], pr[1][3]);
+    x0 *= f0;
+    x1 *= f0;
+    x2 *= f1;
+    x3 *= f1;
+    if constexpr (MASKED) {
+      if (gq >= valid) x0 = x1 = -INFINITY;
+      if (gq + 8 >= valid) x2 = x3 = -INFINITY;
+    }
+    float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);  // heads 2t, 2t+1 over the thread's tokens
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, sh));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, sh));
+    }
+    const float mn0 = fmaxf(m[ng][0], mx0), mn1 = fmaxf(m[ng][1], mx1);  // finite: token 0 is live
+    alpha[ng][0] = fast_exp2(m[ng][0] - mn0);
+    alpha[ng][1] = fast_exp2(m[ng][1] - mn1);
+    moved = moved || alpha[ng][0] != 1.f || alpha[ng][1] != 1.f;
+    m[ng][0] = mn0;
+    m[ng][1] = mn1;
+    const float p0 = fast_exp2(x0 - mn0), p1 = fast_exp2(x1 - mn1);
+    const float p2 = fast_exp2(x2 - mn0), p3 = fast_exp2(x3 - mn1);
+    l[ng][0] = l[ng][0] * alpha[ng][0] + (p0 + p2);
+    l[ng][1] = l[ng][1] * alpha[ng][1] + (p1 + p3);
+    // (token g | g+8, heads 2t, 2t+1) -> (tokens 2t, 2t+1 | 2t+8, 2t+9, head g)
+    pb[ng][0] = movmatrix_trans(SCALED ? pack_half2(p0 * vs0, p1 * vs0) : pack_half2(p0, p1));
+    pb[ng][1] = movmatrix_trans(SCALED ? pack_half2(p2 * vs1, p3 * vs1) : pack_half2(p2, p3));
   }
-  l0 = l0 * a0 + ps0;
-  l1 = l1 * a1 + ps1;
   // the running maxima settle after the first tiles; skip the rescale when nobody's moved
-  if (__any_sync(kFull, a0 != 1.f || a1 != 1.f)) {
+  if (__any_sync(kFull, moved)) {
 #pragma unroll
-    for (int n = 0; n < C::NT; ++n) {
-      o[n][0] *= a0;
-      o[n][1] *= a0;
-      o[n][2] *= a1;
-      o[n][3] *= a1;
+    for (int mt = 0; mt < C::MT; ++mt) {
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) {
+        o[mt][ng][0] *= alpha[ng][0];
+        o[mt][ng][1] *= alpha[ng][1];
+        o[mt][ng][2] *= alpha[ng][0];
+        o[mt][ng][3] *= alpha[ng][1];
+      }
     }
   }
 
-  // ---- O += P V ---------------------------------------------------------------------------------
+  // ---- O^T += V^T P^T ---------------------------------------------------------------------------
   // Rows of V past `valid` hold whatever the page holds.  Every int8 byte is a finite number,
   // so P = 0 already removes it; f16 / e5m2 garbage may be NaN and is zeroed in masked tiles.
   constexpr bool kMaskV = MASKED && KV != PD_KV_I8;
-  uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2tq, 2tq+1), (2tq+8, 2tq+9)
+  uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2t, 2t+1), (2t+8, 2t+9)
   if constexpr (kMaskV) {
     keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
     keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
   }
   if constexpr (KV == PD_KV_F16) {
-    // transposed 8x8 matrices: (tokens 0-7, chunk nd), (8-15, nd), (0-7, nd+1), (8-15, nd+1)
+    // transposed 8x8 matrices (tokens 0-7, lo), (0-7, hi), (8-15, lo), (8-15, hi) of the 16
+    // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
     const int mi = lane >> 3;
-    const int token = 8 * (mi & 1) + (lane & 7);
+    const int token = 8 * (mi >> 1) + (lane & 7);
     const uint32_t row = vbase + token * 128;
 #pragma unroll
-    for (int nd = 0; nd < C::NT; nd += 2) {
-      const int chunk = (nd & 7) + (mi >> 1);
-      uint32_t b[4];
-      ldmatrix_x4_trans(row + (nd >> 3) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), b);
+    for (int mt = 0; mt < C::MT; ++mt) {
+      const int chunk = ((2 * mt) & 7) + (mi & 1);
+      uint32_t a[4];
+      ldmatrix_x4_trans(row + (mt >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
       if constexpr (kMaskV) {
-        b[0] &= keep_lo;
-        b[1] &= keep_hi;
-        b[2] &= keep_lo;
-        b[3] &= keep_hi;
+        a[0] &= keep_lo;
+        a[1] &= keep_lo;
+        a[2] &= keep_hi;
+        a[3] &= keep_hi;
       }
-      mma_f16(o[nd], pa, b[0], b[1]);
-      mma_f16(o[nd + 1], pa, b[2], b[3]);
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) mma_f16(o[mt][ng], a, pb[ng][0], pb[ng][1]);
     }
   } else {
-    // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of columns
-    // 4*(gq + 8*jj) .. +3 and transposes bytes in registers.  Output n-tile 4*jj + i then holds
-    // head_dim column 32*jj + 4*c + i for fragment column c; the epilogue undoes it.
+    // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of head_dim
+    // columns 32*jj + 4*g .. +3 and transposes bytes in registers.  m-tile 2*jj + h then holds
+    // column 32*jj + 4*g + 2*h in its row g and column + 1 in its row g + 8; the epilogue
+    // writes them back in order.
     const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
 #pragma unroll
     for (int jj = 0; jj < D / 32; ++jj) {
@@ -440,17 +452,18 @@ __device__ __forceinline__ void consume_tile(
       // bytes (c0, c2) and (c1, c3) of the token pairs side by side
       const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
       const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
-      uint32_t b[4][2] = {{cvt_pair<KV>(e01, false), cvt_pair<KV>(e23, false)},
-                          {cvt_pair<KV>(o01, false), cvt_pair<KV>(o23, false)},
-                          {cvt_pair<KV>(e01, true), cvt_pair<KV>(e23, true)},
-                          {cvt_pair<KV>(o01, true), cvt_pair<KV>(o23, true)}};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int h = 0; h < 2; ++h) {
+        uint32_t a[4] = {cvt_pair<KV>(e01, h != 0), cvt_pair<KV>(o01, h != 0),
+                         cvt_pair<KV>(e23, h != 0), cvt_pair<KV>(o23, h != 0)};
         if constexpr (kMaskV) {
-          b[i][0] &= keep_lo;
-          b[i][1] &= keep_hi;
+          a[0] &= keep_lo;
+          a[1] &= keep_lo;
+          a[2] &= keep_hi;
+          a[3] &= keep_hi;
         }
-        mma_f16(o[4 * jj + i], pa, b[i][0], b[i][1]);
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng) mma_f16(o[2 * jj + h][ng], a, pb[ng][0], pb[ng][1]);
       }
     }
   }
@@ -459,7 +472,7 @@ __device__ __forceinline__ void consume_tile(
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
-template <int KV, int D, int HB, bool SCALED>
+template <int KV, int D, int HB, bool SCALED, int NG>
 __global__ void __launch_bounds__(StreamCfg<KV, D, HB, SCALED>::THREADS, 1)
 stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v) {
@@ -632,57 +645,63 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
     const bool whole = (j == 0) && (seg_end == vend) && (sp.splits == 1);
     const int kvh = vi.hb * HB + role;
 
-    // ---- query rows of this kv head's group as A fragments (rows >= group are zero) ---------
-    uint32_t qa[C::KSTEPS][4];
-    {
-      const __half* qrow0 = (const __half*)p.q + (int64_t)vi.b * p.q_sb +
-                            (int64_t)(kvh * p.group + gq) * p.q_sh;
-      const __half* qrow1 = qrow0 + 8 * p.q_sh;
-      const bool r0 = gq < p.group, r1 = gq + 8 < p.group;
+    // ---- query rows of this kv head's group as B fragments: thread (g, t) holds head g (+8 per
+    // n-tile), head_dim pairs of its k slots; heads >= group are zero --------------------------
+    uint32_t qb[C::KSTEPS][NG][2];
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+      const int head = 8 * ng + gq;
+      const bool live = head < p.group;
+      const __half* qrow = (const __half*)p.q + (int64_t)vi.b * p.q_sb +
+                           (int64_t)(kvh * p.group + (live ? head : 0)) * p.q_sh;
 #pragma unroll
       for (int ks = 0; ks < C::KSTEPS; ++ks) {
-        int c_lo, c_hi;  // head_dim index of fragment columns (2tq, 2tq+1) and (2tq+8, 2tq+9)
+        int c_lo, c_hi;  // head_dim index of k slots (2t, 2t+1) and (2t+8, 2t+9)
         if constexpr (KV == PD_KV_F16) {
           c_lo = 16 * ks + 2 * tq;
           c_hi = c_lo + 8;
         } else {
-          // 8-bit rows are read as 16-byte chunks 2tq and 2tq+1; k-step ks uses word ks % 4 of
-          // chunk 2tq + ks / 4, whose four elements fill the thread's four k slots
+          // 8-bit rows are read as 16-byte chunks 2t and 2t+1; k-step ks uses word ks % 4 of
+          // chunk 2t + ks / 4, whose four elements fill the thread's four k slots
           c_lo = 32 * tq + 16 * (ks >> 2) + 4 * (ks & 3);
           c_hi = c_lo + 2;
         }
-        qa[ks][0] = r0 ? __ldg(reinterpret_cast<const uint32_t*>(qrow0 + c_lo)) : 0u;
-        qa[ks][1] = r1 ? __ldg(reinterpret_cast<const uint32_t*>(qrow1 + c_lo)) : 0u;
-        qa[ks][2] = r0 ? __ldg(reinterpret_cast<const uint32_t*>(qrow0 + c_hi)) : 0u;
-        qa[ks][3] = r1 ? __ldg(reinterpret_cast<const uint32_t*>(qrow1 + c_hi)) : 0u;
+        qb[ks][ng][0] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_lo)) : 0u;
+        qb[ks][ng][1] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_hi)) : 0u;
+      }
+    }
+    // int8 keys are fed to the tensor core as 1152 + x (cvt_pair_biased); the surplus
+    // 1152 * sum_d q[head][d] is removed from the scores of heads 2t and 2t+1 afterwards
+    float qbias[NG][2];
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+      qbias[ng][0] = qbias[ng][1] = 0.f;
+      if constexpr (KV == PD_KV_I8) {
+        float hs = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < C::KSTEPS; ++ks) {
+          const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][0]));
+          const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][1]));
+          hs += (x.x + x.y) + (y.x + y.y);
+        }
+        hs += __shfl_xor_sync(kFull, hs, 1);
+        hs += __shfl_xor_sync(kFull, hs, 2);  // sum over head_dim of head g
+        qbias[ng][0] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq));
+        qbias[ng][1] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq + 1));
       }
     }
 
-    // int8 keys are fed to the tensor core as 1152 + x (see cvt_pair_biased); the surplus
-    // 1152 * sum_d q[row][d] is removed from the scores afterwards
-    float qbias0 = 0.f, qbias1 = 0.f;
-    if constexpr (KV == PD_KV_I8) {
+    float m[NG][2], l[NG][2];
+    float o[C::MT][NG][4];
 #pragma unroll
-      for (int ks = 0; ks < C::KSTEPS; ++ks) {
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][0]));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][1]));
-        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][2]));
-        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][3]));
-        qbias0 += (a.x + a.y) + (c.x + c.y);
-        qbias1 += (b.x + b.y) + (d.x + d.y);
-      }
-      qbias0 += __shfl_xor_sync(kFull, qbias0, 1);
-      qbias0 += __shfl_xor_sync(kFull, qbias0, 2);
-      qbias1 += __shfl_xor_sync(kFull, qbias1, 1);
-      qbias1 += __shfl_xor_sync(kFull, qbias1, 2);
-      qbias0 *= 1152.f;
-      qbias1 *= 1152.f;
+    for (int ng = 0; ng < NG; ++ng) {
+      m[ng][0] = m[ng][1] = -INFINITY;
+      l[ng][0] = l[ng][1] = 0.f;
     }
-
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    float o[C::NT][4];
 #pragma unroll
-    for (int n = 0; n < C::NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    for (int mt = 0; mt < C::MT; ++mt)
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) o[mt][ng][0] = o[mt][ng][1] = o[mt][ng][2] = o[mt][ng][3] = 0.f;
 
     for (; g < seg_end; ++g, ++j, ++it) {
       const int st = it % nstage;
@@ -696,75 +715,72 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         const uint32_t scales = sbase + 2 * C::TILE_BYTES + kvh * 2;
         const int remaining = vi.hi - (vi.lo + j * kTileTokens);
         if (remaining >= kTileTokens)
-          consume_tile<KV, D, HB, SCALED, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2, lane,
-                                                 qa, qbias0, qbias1, m0, m1, l0, l1, o);
+          consume_tile<KV, D, HB, SCALED, NG, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2,
+                                                     lane, qb, qbias, m, l, o);
         else
-          consume_tile<KV, D, HB, SCALED, true>(kbase, scales, p.hkv, remaining, p.scale_log2, lane, qa,
-                                                qbias0, qbias1, m0, m1, l0, l1, o);
+          consume_tile<KV, D, HB, SCALED, NG, true>(kbase, scales, p.hkv, remaining, p.scale_log2,
+                                                    lane, qb, qbias, m, l, o);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * st);
     }
     if (aborted) break;
 
-    // ---- segment epilogue ---------------------------------------------------------------------
-    l0 += __shfl_xor_sync(kFull, l0, 1);
-    l0 += __shfl_xor_sync(kFull, l0, 2);
-    l1 += __shfl_xor_sync(kFull, l1, 1);
-    l1 += __shfl_xor_sync(kFull, l1, 2);
+    // ---- segment epilogue: the thread owns heads 2t, 2t+1 (+8 per n-tile) -----------------------
     const float unscale = SCALED ? (1.f / 256.f) : 1.f;
-    const float inv0 = l0 > 0.f ? unscale / l0 : 0.f, inv1 = l1 > 0.f ? unscale / l1 : 0.f;
-    const float lse0 = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
-    const float lse1 = l1 > 0.f ? m1 + log2f(l1) : -INFINITY;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int rrow = gq + 8 * half;
-      if (rrow >= p.group) continue;
-      const float inv = half ? inv1 : inv0;
-      const float lse = half ? lse1 : lse0;
-      const int hq = kvh * p.group + rrow;
-      __half* dst16 = nullptr;
-      float* dst32 = nullptr;
-      if (whole) {
-        if (p.out) dst16 = (__half*)p.out + (int64_t)vi.b * p.o_sb + (int64_t)hq * p.o_sh;
-        if (p.res_o) {
-          dst32 = p.res_o + ((int64_t)vi.b * p.hq + hq) * D;
-          if (tq == 0) p.res_lse[(int64_t)vi.b * p.hq + hq] = lse;
-        }
-      } else {
-        const int64_t slot_row = (int64_t)(w + v) * hg + role * p.group + rrow;
-        dst32 = p.part_o + slot_row * D;
-        if (tq == 0) p.part_lse[slot_row] = lse;
-      }
-      if constexpr (KV == PD_KV_F16) {
+    for (int ng = 0; ng < NG; ++ng) {
 #pragma unroll
-        for (int n = 0; n < C::NT; ++n) {
-          const int col = 8 * n + 2 * tq;
-          const float x = o[n][2 * half] * inv, y = o[n][2 * half + 1] * inv;
-          if (dst16) *reinterpret_cast<__half2*>(dst16 + col) = __floats2half2_rn(x, y);
-          if (dst32) *reinterpret_cast<float2*>(dst32 + col) = make_float2(x, y);
-        }
-      } else {
+      for (int e = 0; e < 2; ++e) {
+        float lsum = l[ng][e];
 #pragma unroll
-        for (int jj = 0; jj < D / 32; ++jj) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            e[i] = o[4 * jj + i][2 * half] * inv;          // fragment column 2tq
-            e[4 + i] = o[4 * jj + i][2 * half + 1] * inv;  // fragment column 2tq + 1
+        for (int sh = 4; sh < 32; sh <<= 1) lsum += __shfl_xor_sync(kFull, lsum, sh);
+        const int head = 8 * ng + 2 * tq + e;
+        if (head >= p.group) continue;
+        const float inv = lsum > 0.f ? unscale / lsum : 0.f;
+        const float lse = lsum > 0.f ? m[ng][e] + log2f(lsum) : -INFINITY;
+        const int hq = kvh * p.group + head;
+        __half* dst16 = nullptr;
+        float* dst32 = nullptr;
+        if (whole) {
+          if (p.out) dst16 = (__half*)p.out + (int64_t)vi.b * p.o_sb + (int64_t)hq * p.o_sh;
+          if (p.res_o) {
+            dst32 = p.res_o + ((int64_t)vi.b * p.hq + hq) * D;
+            if (gq == 0) p.res_lse[(int64_t)vi.b * p.hq + hq] = lse;
           }
-          const int col = 32 * jj + 8 * tq;
-          if (dst16) {
-            uint4 pk;
-            pk.x = pack_half2(e[0], e[1]);
-            pk.y = pack_half2(e[2], e[3]);
-            pk.z = pack_half2(e[4], e[5]);
-            pk.w = pack_half2(e[6], e[7]);
-            *reinterpret_cast<uint4*>(dst16 + col) = pk;
+        } else {
+          const int64_t slot_row = (int64_t)(w + v) * hg + role * p.group + head;
+          dst32 = p.part_o + slot_row * D;
+          if (gq == 0) p.part_lse[slot_row] = lse;
+        }
+        if constexpr (KV == PD_KV_F16) {
+          // m-tile mt holds head_dim 16*mt + g (regs 0, 1) and 16*mt + g + 8 (regs 2, 3)
+#pragma unroll
+          for (int mt = 0; mt < C::MT; ++mt) {
+            const float x = o[mt][ng][e] * inv, y = o[mt][ng][2 + e] * inv;
+            const int col = 16 * mt + gq;
+            if (dst16) {
+              dst16[col] = __float2half_rn(x);
+              dst16[col + 8] = __float2half_rn(y);
+            }
+            if (dst32) {
+              dst32[col] = x;
+              dst32[col + 8] = y;
+            }
           }
-          if (dst32) {
-            *reinterpret_cast<float4*>(dst32 + col) = make_float4(e[0], e[1], e[2], e[3]);
-            *reinterpret_cast<float4*>(dst32 + col + 4) = make_float4(e[4], e[5], e[6], e[7]);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < D / 32; ++jj) {
+            const float x0 = o[2 * jj][ng][e] * inv, x1 = o[2 * jj][ng][2 + e] * inv;
+            const float x2 = o[2 * jj + 1][ng][e] * inv, x3 = o[2 * jj + 1][ng][2 + e] * inv;
+            const int col = 32 * jj + 4 * gq;
+            if (dst16) {
+              uint2 pk;
+              pk.x = pack_half2(x0, x1);
+              pk.y = pack_half2(x2, x3);
+              *reinterpret_cast<uint2*>(dst16 + col) = pk;
+            }
+            if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
           }
         }
       }
@@ -1007,11 +1023,11 @@ static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
   return true;
 }
 
-template <int KV, int D, int HB, bool SCALED>
-static cudaError_t launch_one(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                              int grid, uint32_t smem, cudaStream_t st) {
+template <int KV, int D, int HB, bool SCALED, int NG>
+static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                             int grid, uint32_t smem, cudaStream_t st) {
   using C = StreamCfg<KV, D, HB, SCALED>;
-  auto* kern = stream_decode_kernel<KV, D, HB, SCALED>;
+  auto* kern = stream_decode_kernel<KV, D, HB, SCALED, NG>;
   static bool configured[64] = {};  // per device: the opt-in shared-memory limit has been raised
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorInvalidDevice;
@@ -1022,6 +1038,14 @@ static cudaError_t launch_one(const StreamParams& sp, const CUtensorMap& mk, con
   }
   kern<<<grid, C::THREADS, smem, st>>>(sp, mk, mv);
   return cudaGetLastError();
+}
+
+// groups of up to 8 query heads fit one 8-wide n-tile, up to 16 need two
+template <int KV, int D, int HB, bool SCALED>
+static cudaError_t launch_one(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                              int grid, uint32_t smem, cudaStream_t st) {
+  return sp.p.group <= 8 ? launch_ng<KV, D, HB, SCALED, 1>(sp, mk, mv, grid, smem, st)
+                         : launch_ng<KV, D, HB, SCALED, 2>(sp, mk, mv, grid, smem, st);
 }
 
 template <int KV, int D, bool SCALED>

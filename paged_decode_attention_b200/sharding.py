@@ -119,7 +119,7 @@ class KVRangeShardedDecoder:
         b, hq, d = self.q.shape
         self.decode_fn(self.q, self.cache, self.f32, self.lse, self.kernel)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+            dist.all_gather_into_tensor(self.gathered.view(-1), self.local, group=self.group)
         else:
             self.gathered[0].copy_(self.local)
         parts = self.gathered[:, : self.n_o].view(self.world, b, hq, d)

@@ -169,6 +169,18 @@ def test_fp32_result_and_lse(name, kernel):
     assert np.abs(lse.cpu().numpy() - ref_lse).max() < 5e-3
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("hq,hkv,d,kv_dtype", [(32, 2, 128, "fp16"), (24, 2, 128, "int8"), (12, 1, 64, "fp16"),
+                                               (48, 4, 128, "fp8_e5m2")])
+def test_wide_groups(hq, hkv, d, kv_dtype, kernel):
+    """Groups of 9..16 query heads per kv head (two n-tiles in the streaming kernel)."""
+    case = cases.Case("wide", hq, hkv, d, 16, kv_dtype, (333, 1, 1500), seed=31)
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(q_np.astype(np.float32), oc)
+    for splits in (None, 3):
+        helpers.assert_close(_run(case, kernel, splits), ref, what=f"group {hq // hkv} {kv_dtype}")
+
+
 def test_merge_partials_matches_oracle():
     rng = np.random.Generator(np.random.PCG64(77))
     po_ = rng.standard_normal((5, 3, 14, 64), dtype=np.float32)
