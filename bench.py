@@ -2,7 +2,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
 
-One step is one decode call (the streaming decode kernel plus its merge kernel) over one
+One step is one decode call (one launch of the streaming decode kernel, which merges its own
+partial results) over one
 synthetic batch of the named workload.  At N GPUs every rank holds its own batch of the
 same shape (requests shard across ranks with no communication: weak scaling), except
 workload c4, whose KV range is sharded across ranks and merged after an all-gather
@@ -223,7 +224,7 @@ def run_ours(args) -> None:
                                   num_splits=args.num_splits if args.num_splits else None)
         step = prepared.step
 
-        launches_per_step = 2 if (kernel_used == "stream" or pdec.workspace_bytes(dargs) > 0) else 1
+        launches_per_step = 1 if (kernel_used == "stream" or pdec.workspace_bytes(dargs) == 0) else 2
     my_bytes = cache.bytes_read_per_decode_step()
     resident = sum(t.numel() * t.element_size() for t in (cache.k_cache, cache.v_cache))
 

@@ -203,7 +203,7 @@ PD_API int pd_gather(const PdGatherArgs* args);
  * engine owns the allocator and forbids allocation on the decode path; a host with no
  * allocator of its own at all (a thin C or FFI caller that only holds the pointers it was
  * given).  Such callers pass q, out and the cache exactly as for pd_decode and leave
- * `workspace` NULL (it is ignored); the streaming kernel's plan and partial-result slots live
+ * `workspace` NULL (it is ignored); the streaming kernel's arrival counters and partial-result slots live
  * in a fixed PD_STATIC_SCRATCH_BYTES array compiled into the library, which every GPU that
  * loads the library holds until the process exits.
  *
@@ -214,8 +214,8 @@ PD_API int pd_gather(const PdGatherArgs* args);
  *   - the first call on each device looks up the array's device address; make that first call
  *     before any stream capture begins;
  *   - all calls on a device share the one array and it keeps the previous call's contents.
- *     Nothing in it has to be cleared between calls (every word read is written first within
- *     the call), but two calls whose kernels can overlap on the GPU (different streams, or
+ *     The caller clears nothing (each call zeroes the few counters it needs, on its stream,
+ *     and writes every other word before reading it), but two calls whose kernels can overlap on the GPU (different streams, or
  *     different host threads on different streams) race on it: keep calls on one stream or
  *     order them yourself;
  *   - no cudaMalloc, cudaFree or other allocating routine is called, host heap included.

@@ -24,8 +24,10 @@
 //
 // Results.  A (worker, virtual sequence) segment that covers a whole unsplit request writes
 // its output row directly; any other segment writes a normalised fp32 partial plus its base-2
-// log-sum-exp into slot (worker + virtual sequence) of the scratch, and the merge kernel
-// combines a request's slots (pagedattn/triton_decode.py:221-240).
+// log-sum-exp into slot (worker + virtual sequence) of the scratch and takes a ticket on the
+// (request, kv head) counter; the warp whose ticket completes the count merges the request's
+// slots in place (pagedattn/triton_decode.py:221-240).  No second kernel, and no warp ever
+// waits for another.
 //
 // Every wait is bounded: a wait that exceeds its limit sets PD_DEV_TIMEOUT in the status word,
 // raises the CTA's abort flag, and all warps leave their loops; the producer then waits (again
@@ -43,22 +45,30 @@ namespace pd {
 // configuration
 // ---------------------------------------------------------------------------------------------
 constexpr int kTileTokens = 16;
+
+// 16-bit page element types: both are moved and multiplied as they are
+__host__ __device__ constexpr bool is_16bit(int kv) { return kv == PD_KV_F16 || kv == PD_KV_BF16; }
 constexpr int kMaxVseq = 4096;
 constexpr int kMinTilesPerWorker = 4;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxStages = 12;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
+// Workers per CTA: eight consumer warps' worth (at most four workers).  Kernels for 8-bit pages
+// with eight heads per block also exist with two workers (sixteen consumer warps): an 8-bit tile
+// carries half the bytes for the same instruction count, and the extra warps hide the
+// conversion latency.  Every worker adds a segment to each request it touches, so the host
+// picks two only for batches with many requests (see derive()).
+__host__ __device__ constexpr int base_workers_per_cta(int hb) { return 8 / hb < 4 ? 8 / hb : 4; }
+
 template <int KV, int D, int HB, bool SCALED>
 struct StreamCfg {
-  static constexpr int EB = (KV == PD_KV_F16) ? 2 : 1;
+  static constexpr int EB = is_16bit(KV) ? 2 : 1;
   static constexpr int ROWB = D * EB;
   static_assert(ROWB == 128 || ROWB == 256, "row must be one or two 128-byte chunks");
   static constexpr int NC = ROWB / 128;                     // 128-byte chunks per row
   static constexpr int BOX_ELEMS = 128 / EB;                // elements of one chunk
-  static constexpr int WPC = (8 / HB) < 4 ? (8 / HB) : 4;   // workers per CTA
   static constexpr int WARPS_PER_WORKER = HB + 1;
-  static constexpr int THREADS = WPC * WARPS_PER_WORKER * 32;
   static constexpr int CHUNK_BYTES = HB * kTileTokens * 128; // one TMA box
   static constexpr int TILE_BYTES = NC * CHUNK_BYTES;        // K (or V) of one tile
   static constexpr int SCALE_BYTES = SCALED ? 2048 : 0;      // K scales at +0, V scales at +1024
@@ -69,21 +79,10 @@ struct StreamCfg {
 
 struct StreamParams {
   Params p;
-  int32_t nvseq, nhb, splits, nstage;
+  int32_t nvseq, nhb, splits, nstage, wpc;
   uint32_t bar_off, meta_off, misc_off, prefix_off;
-  int32_t* plan;  // [0] tiles per worker, [1] total tiles, [2 + v] prefix of virtual sequence v
+  int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
   uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
-};
-
-struct MergeSlotsParams {
-  const int32_t* plan;
-  const float* part_o;
-  const float* part_lse;
-  int32_t batch, hq, group, hb_heads, splits, d;
-  void* out;
-  int64_t o_sb, o_sh;
-  float* res_o;
-  float* res_lse;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -200,9 +199,41 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// the same with bf16 inputs
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// bf16 pages are multiplied as bf16 (q, P and the output are bf16 too); every other page type
+// reaches the tensor core as f16
+template <int KV>
+__device__ __forceinline__ void mma_kv(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (KV == PD_KV_BF16) mma_bf16(c, a, b0, b1);
+  else mma_f16(c, a, b0, b1);
+}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Two floats -> packed 16-bit pair in the type q and out use (bf16 with bf16 pages, else f16).
+template <int KV>
+__device__ __forceinline__ uint32_t pack_io2(float lo, float hi) {
+  if constexpr (KV == PD_KV_BF16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    return pack_half2(lo, hi);
+  }
+}
+template <int KV>
+__device__ __forceinline__ void store_io(void* row, int col, float x) {
+  if constexpr (KV == PD_KV_BF16) ((__nv_bfloat16*)row)[col] = __float2bfloat16_rn(x);
+  else ((__half*)row)[col] = __float2half_rn(x);
 }
 
 // Two stored 8-bit elements (bytes `lo_sel`, `lo_sel + 1` of w) -> packed f16x2, exactly.
@@ -296,7 +327,7 @@ __device__ __forceinline__ void consume_tile(
   float s[NG][4];
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) s[ng][0] = s[ng][1] = s[ng][2] = s[ng][3] = 0.f;
-  if constexpr (KV == PD_KV_F16) {
+  if constexpr (is_16bit(KV)) {
     // A fragments by ldmatrix: matrices (tokens 0-7, lo), (8-15, lo), (0-7, hi), (8-15, hi) where
     // lo/hi are the two 16-byte chunks of the k-step
     const int mi = lane >> 3;
@@ -308,7 +339,7 @@ __device__ __forceinline__ void consume_tile(
       uint32_t a[4];
       ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_f16(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
+      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
     }
   } else {
     // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each row give
@@ -336,7 +367,7 @@ __device__ __forceinline__ void consume_tile(
           a[3] = cvt_pair<KV>(w1[i], true);
         }
 #pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_f16(s[ng], a, qb[4 * jh + i][ng][0], qb[4 * jh + i][ng][1]);
+        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * jh + i][ng][0], qb[4 * jh + i][ng][1]);
       }
     }
   }
@@ -388,8 +419,8 @@ __device__ __forceinline__ void consume_tile(
     l[ng][0] = l[ng][0] * alpha[ng][0] + (p0 + p2);
     l[ng][1] = l[ng][1] * alpha[ng][1] + (p1 + p3);
     // (token g | g+8, heads 2t, 2t+1) -> (tokens 2t, 2t+1 | 2t+8, 2t+9, head g)
-    pb[ng][0] = movmatrix_trans(SCALED ? pack_half2(p0 * vs0, p1 * vs0) : pack_half2(p0, p1));
-    pb[ng][1] = movmatrix_trans(SCALED ? pack_half2(p2 * vs1, p3 * vs1) : pack_half2(p2, p3));
+    pb[ng][0] = movmatrix_trans(SCALED ? pack_io2<KV>(p0 * vs0, p1 * vs0) : pack_io2<KV>(p0, p1));
+    pb[ng][1] = movmatrix_trans(SCALED ? pack_io2<KV>(p2 * vs1, p3 * vs1) : pack_io2<KV>(p2, p3));
   }
   // the running maxima settle after the first tiles; skip the rescale when nobody's moved
   if (__any_sync(kFull, moved)) {
@@ -414,7 +445,7 @@ __device__ __forceinline__ void consume_tile(
     keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
     keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
   }
-  if constexpr (KV == PD_KV_F16) {
+  if constexpr (is_16bit(KV)) {
     // transposed 8x8 matrices (tokens 0-7, lo), (0-7, hi), (8-15, lo), (8-15, hi) of the 16
     // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
     const int mi = lane >> 3;
@@ -432,7 +463,7 @@ __device__ __forceinline__ void consume_tile(
         a[3] &= keep_hi;
       }
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_f16(o[mt][ng], a, pb[ng][0], pb[ng][1]);
+      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
     }
   } else {
     // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of head_dim
@@ -454,8 +485,24 @@ __device__ __forceinline__ void consume_tile(
       const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t a[4] = {cvt_pair<KV>(e01, h != 0), cvt_pair<KV>(o01, h != 0),
-                         cvt_pair<KV>(e23, h != 0), cvt_pair<KV>(o23, h != 0)};
+        uint32_t a[4];
+        if constexpr (KV == PD_KV_I8) {
+          // int8 values enter as 1152 + x (one prmt each); a second mma with the constant
+          // -1152 on the same P^T takes the surplus out again inside the accumulator, tile by
+          // tile, so the sum never carries the bias
+          a[0] = cvt_pair_biased(e01, h != 0);
+          a[1] = cvt_pair_biased(o01, h != 0);
+          a[2] = cvt_pair_biased(e23, h != 0);
+          a[3] = cvt_pair_biased(o23, h != 0);
+          const uint32_t neg[4] = {0xE480E480u, 0xE480E480u, 0xE480E480u, 0xE480E480u};
+#pragma unroll
+          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], neg, pb[ng][0], pb[ng][1]);
+        } else {
+          a[0] = cvt_pair<KV>(e01, h != 0);
+          a[1] = cvt_pair<KV>(o01, h != 0);
+          a[2] = cvt_pair<KV>(e23, h != 0);
+          a[3] = cvt_pair<KV>(o23, h != 0);
+        }
         if constexpr (kMaskV) {
           a[0] &= keep_lo;
           a[1] &= keep_lo;
@@ -463,21 +510,124 @@ __device__ __forceinline__ void consume_tile(
           a[3] &= keep_hi;
         }
 #pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_f16(o[2 * jj + h][ng], a, pb[ng][0], pb[ng][1]);
+        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], a, pb[ng][0], pb[ng][1]);
       }
     }
+  }
+}
+
+// Segments (worker, virtual sequence) that cover request b / head block hb, in the order the
+// merge visits them: for every split with tiles, the workers first .. last of its tile range.
+template <typename F>
+__device__ __forceinline__ void for_each_segment(const int* prefix, int per, int v0, int splits, F&& f) {
+  for (int s = 0; s < splits; ++s) {
+    const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
+    if (last <= first) continue;
+    for (int wk = first / per; wk <= (last - 1) / per; ++wk) f(wk + v0 + s);
+  }
+}
+
+// Log-sum-exp merge of every partial of one (request, kv head), run by the consumer warp whose
+// partial arrived last (pagedattn/triton_decode.py:221-240 for the arithmetic).  The eight
+// 4-lane groups of the warp are split between rows and segments: with RP = the group size
+// rounded up to a power of two (at most 8), lane group q handles row q % RP and the segments
+// i with i % (8 / RP) == q / RP; a lane owns the head_dim floats 16*j + 4*c .. +3 of its row.
+// Small groups thus spread a long segment list (dozens for one long-context request) over more
+// lanes.  The per-phase sums are combined with shuffles.  Partials were written by other SMs:
+// they are read with ld.global.cg after the ticket's fence.
+template <int KV, int D>
+__device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, int per, int v0,
+                                           int splits, int hg, int head_in_block, int b, int kvh,
+                                           int lane) {
+  constexpr int J = D / 16;
+  constexpr unsigned kFull = 0xffffffffu;
+  const int q = lane >> 2, c = lane & 3;
+  int rp = 1;
+  while (rp < p.group && rp < 8) rp <<= 1;
+  const int sp_n = 8 / rp;        // segment phases
+  const int phase = q / rp;
+  for (int r0 = 0; r0 < p.group; r0 += 8) {
+    const int row = r0 + q % rp;
+    const bool live = row < p.group;
+    const int64_t local = (int64_t)head_in_block * p.group + (live ? row : 0);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) {
+      const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
+      if (last <= first) continue;
+      const int slot0 = first / per + v0 + s, n = (last - 1) / per - first / per + 1;
+      const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
+#pragma unroll 4
+      for (int i = phase; i < n; i += sp_n) m = fmaxf(m, __ldcg(lp + (int64_t)i * hg));
+    }
+    for (int sh = 4 * rp; sh < 32; sh <<= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, sh));
+    float denom = 0.f;
+    float acc[J][4];
+#pragma unroll
+    for (int j = 0; j < J; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    if (m > -INFINITY) {
+      for (int s = 0; s < splits; ++s) {
+        const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
+        if (last <= first) continue;
+        const int slot0 = first / per + v0 + s, n = (last - 1) / per - first / per + 1;
+        const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
+        const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
+#pragma unroll 2
+        for (int i = phase; i < n; i += sp_n) {
+          const float lse = __ldcg(lp + (int64_t)i * hg);
+          float4 x[J];
+#pragma unroll
+          for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * hg * (D / 4) + 4 * j);
+          const float wgt = lse > -INFINITY ? exp2f(lse - m) : 0.f;
+          denom += wgt;
+#pragma unroll
+          for (int j = 0; j < J; ++j) {
+            acc[j][0] = fmaf(wgt, x[j].x, acc[j][0]);
+            acc[j][1] = fmaf(wgt, x[j].y, acc[j][1]);
+            acc[j][2] = fmaf(wgt, x[j].z, acc[j][2]);
+            acc[j][3] = fmaf(wgt, x[j].w, acc[j][3]);
+          }
+        }
+      }
+    }
+    for (int sh = 4 * rp; sh < 32; sh <<= 1) {
+      denom += __shfl_xor_sync(kFull, denom, sh);
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] += __shfl_xor_sync(kFull, acc[j][e], sh);
+      }
+    }
+    if (!live || phase != 0) continue;
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    const int hq = kvh * p.group + row;
+    __half* dst16 = p.out ? (__half*)p.out + (int64_t)b * p.o_sb + (int64_t)hq * p.o_sh : nullptr;
+    float* dst32 = p.res_o ? p.res_o + ((int64_t)b * p.hq + hq) * D : nullptr;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int col = 16 * j + 4 * c;
+      const float x0 = acc[j][0] * inv, x1 = acc[j][1] * inv, x2 = acc[j][2] * inv, x3 = acc[j][3] * inv;
+      if (dst16) {
+        uint2 pk;
+        pk.x = pack_io2<KV>(x0, x1);
+        pk.y = pack_io2<KV>(x2, x3);
+        *reinterpret_cast<uint2*>(dst16 + col) = pk;
+      }
+      if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
+    }
+    if (p.res_o && c == 0) p.res_lse[(int64_t)b * p.hq + hq] = denom > 0.f ? m + log2f(denom) : -INFINITY;
   }
 }
 
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
-template <int KV, int D, int HB, bool SCALED, int NG>
-__global__ void __launch_bounds__(StreamCfg<KV, D, HB, SCALED>::THREADS, 1)
+template <int KV, int D, int HB, bool SCALED, int NG, int WPC>
+__global__ void __launch_bounds__(WPC * (HB + 1) * 32, 1)
 stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kThreads = WPC * (HB + 1) * 32;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
@@ -497,7 +647,7 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
 
   // ---- tiles per virtual sequence, then an inclusive scan: prefix[v] = first tile of v ------
   const int nv = sp.nvseq;
-  for (int v = tid; v < nv; v += C::THREADS) {
+  for (int v = tid; v < nv; v += kThreads) {
     const VseqInfo i = vseq_info(sp, v);
     prefix[v + 1] = i.hi > i.lo ? (i.hi - i.lo + kTileTokens - 1) / kTileTokens : 0;
   }
@@ -531,23 +681,27 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
   __syncthreads();
 
   const int total = prefix[nv];
-  const int workers = gridDim.x * C::WPC;
+  const int workers = gridDim.x * WPC;
   int per = (total + workers - 1) / workers;
   if (per < kMinTilesPerWorker) per = kMinTilesPerWorker;
-  const int w = blockIdx.x * C::WPC + wl;  // global worker id
+  const int w = blockIdx.x * WPC + wl;  // global worker id
   const long long g0l = (long long)w * per;
   const int g0 = g0l < total ? (int)g0l : total;
   const int g1 = g0 + per < total ? g0 + per : total;
   if (blockIdx.x == 0) {
-    // the merge kernel re-derives every segment from this plan
-    if (tid == 0) {
-      sp.plan[0] = per;
-      sp.plan[1] = total;
+    // requests without a single token are nobody's work: their rows are zero, their lse -inf
+    for (int u = tid; u < sp.nhb * p.batch; u += kThreads) {
+      if (prefix[(u + 1) * sp.splits] != prefix[u * sp.splits]) continue;
+      const int b = u % p.batch, hb = u / p.batch;
+      for (int h = hb * HB * p.group; h < (hb + 1) * HB * p.group; ++h) {
+        for (int d = 0; d < D; ++d) {
+          if (p.out) ((uint16_t*)p.out)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] = 0;  // +0 in f16 and bf16
+          if (p.res_o) p.res_o[((int64_t)b * p.hq + h) * D + d] = 0.f;
+        }
+        if (p.res_o) p.res_lse[(int64_t)b * p.hq + h] = -INFINITY;
+      }
     }
-    for (int v = tid; v <= nv; v += C::THREADS) sp.plan[2 + v] = prefix[v];
   }
-  // let the merge kernel's launch overlap this grid (it waits for this grid to finish)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (g0 >= g1) return;  // nothing for this worker (no barrier is used after this point)
 
   // =============================== producer warp =============================================
@@ -657,7 +811,7 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
 #pragma unroll
       for (int ks = 0; ks < C::KSTEPS; ++ks) {
         int c_lo, c_hi;  // head_dim index of k slots (2t, 2t+1) and (2t+8, 2t+9)
-        if constexpr (KV == PD_KV_F16) {
+        if constexpr (is_16bit(KV)) {
           c_lo = 16 * ks + 2 * tq;
           c_hi = c_lo + 8;
         } else {
@@ -753,15 +907,15 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
           dst32 = p.part_o + slot_row * D;
           if (gq == 0) p.part_lse[slot_row] = lse;
         }
-        if constexpr (KV == PD_KV_F16) {
+        if constexpr (is_16bit(KV)) {
           // m-tile mt holds head_dim 16*mt + g (regs 0, 1) and 16*mt + g + 8 (regs 2, 3)
 #pragma unroll
           for (int mt = 0; mt < C::MT; ++mt) {
             const float x = o[mt][ng][e] * inv, y = o[mt][ng][2 + e] * inv;
             const int col = 16 * mt + gq;
             if (dst16) {
-              dst16[col] = __float2half_rn(x);
-              dst16[col + 8] = __float2half_rn(y);
+              store_io<KV>(dst16, col, x);
+              store_io<KV>(dst16, col + 8, y);
             }
             if (dst32) {
               dst32[col] = x;
@@ -776,8 +930,8 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
             const int col = 32 * jj + 4 * gq;
             if (dst16) {
               uint2 pk;
-              pk.x = pack_half2(x0, x1);
-              pk.y = pack_half2(x2, x3);
+              pk.x = pack_io2<KV>(x0, x1);
+              pk.y = pack_io2<KV>(x2, x3);
               *reinterpret_cast<uint2*>(dst16 + col) = pk;
             }
             if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
@@ -785,69 +939,28 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         }
       }
     }
-    ++v;
-  }
-}
-
-// One CTA per (request, query head): merges the slots the plan assigns to the request.  Rows
-// a single unsplit segment covered were written by the decode kernel and are left alone; rows
-// with no tokens become zero.
-__global__ void __launch_bounds__(128) stream_merge_kernel(const MergeSlotsParams mp) {
-  // Launched with programmatic stream serialization: the CTAs may become resident while the
-  // decode grid still runs; nothing of its output is touched before this wait returns.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int row = blockIdx.x;
-  const int b = row / mp.hq, hq = row % mp.hq;
-  const int kvh = hq / mp.group;
-  const int hb = kvh / mp.hb_heads;
-  const int hl = (kvh % mp.hb_heads) * mp.group + hq % mp.group;
-  const int hg = mp.hb_heads * mp.group;
-  const int per = mp.plan[0];
-  const int32_t* prefix = mp.plan + 2;
-  const int v0 = (hb * mp.batch + b) * mp.splits;
-
-  float m = -INFINITY;
-  int count = 0;
-  for (int s = 0; s < mp.splits; ++s) {
-    const int v = v0 + s;
-    const int first = prefix[v], last = prefix[v + 1];
-    if (last <= first) continue;
-    for (int wk = first / per; wk <= (last - 1) / per; ++wk) {
-      m = fmaxf(m, mp.part_lse[(int64_t)(wk + v) * hg + hl]);
-      ++count;
-    }
-  }
-  if (count == 1 && mp.splits == 1) return;
-  float denom = 0.f;
-  if (count > 0 && m > -INFINITY) {
-    for (int s = 0; s < mp.splits; ++s) {
-      const int v = v0 + s;
-      const int first = prefix[v], last = prefix[v + 1];
-      if (last <= first) continue;
-      for (int wk = first / per; wk <= (last - 1) / per; ++wk)
-        denom += exp2f(mp.part_lse[(int64_t)(wk + v) * hg + hl] - m);
-    }
-  }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int d = threadIdx.x; d < mp.d; d += blockDim.x) {
-    float acc = 0.f;
-    if (denom > 0.f) {
-      for (int s = 0; s < mp.splits; ++s) {
-        const int v = v0 + s;
-        const int first = prefix[v], last = prefix[v + 1];
-        if (last <= first) continue;
-        for (int wk = first / per; wk <= (last - 1) / per; ++wk) {
-          const int64_t sr = (int64_t)(wk + v) * hg + hl;
-          const float lse = mp.part_lse[sr];
-          if (lse > -INFINITY) acc += exp2f(lse - m) * mp.part_o[sr * mp.d + d];
-        }
+    if (!whole) {
+      // Ticket: every segment of this (request, kv head) adds one after its partial is visible;
+      // whoever completes the count merges them all.  Nobody waits for anybody.
+      __threadfence();
+      __syncwarp();
+      int last = 0;
+      const int v0 = (vi.hb * p.batch + vi.b) * sp.splits;
+      if (lane == 0) {
+        int expected = 0;
+        for_each_segment(prefix, per, v0, sp.splits, [&](int) { ++expected; });
+        int* ticket = sp.tickets + (int64_t)vi.b * p.hkv + kvh;
+        last = atomicAdd(ticket, 1) + 1 == expected;
+        if (last) *ticket = 0;  // leave the counter as it was found
+      }
+      last = __shfl_sync(kFull, last, 0);
+      if (last) {
+        __threadfence();
+        merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane);
       }
     }
-    const float x = acc * inv;
-    if (mp.out) ((__half*)mp.out)[(int64_t)b * mp.o_sb + (int64_t)hq * mp.o_sh + d] = __float2half_rn(x);
-    if (mp.res_o) mp.res_o[(int64_t)row * mp.d + d] = x;
+    ++v;
   }
-  if (threadIdx.x == 0 && mp.res_lse) mp.res_lse[row] = denom > 0.f ? m + log2f(denom) : -INFINITY;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -870,12 +983,13 @@ static Shape derive(const PdDecodeArgs* a) {
   Shape s;
   s.hb = head_block(a->num_kv_heads);
   s.nhb = a->num_kv_heads / s.hb;
-  s.wpc = 8 / s.hb < 4 ? 8 / s.hb : 4;
+  s.wpc = base_workers_per_cta(s.hb);
   s.splits = a->num_splits > 0 ? a->num_splits : 1;
   const long long nv = (long long)s.nhb * a->batch * s.splits;
   s.nvseq = nv > INT32_MAX ? INT32_MAX : (int)nv;
   s.scaled = a->k_scale != nullptr;
-  const int eb = a->kv_dtype == PD_KV_F16 ? 2 : 1;
+  if (s.hb == 8 && !is_16bit(a->kv_dtype) && nv >= 64) s.wpc = 2;
+  const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   const int nc = a->head_dim * eb / 128;
   s.stage_bytes = 2 * nc * s.hb * kTileTokens * 128 + (s.scaled ? 2048 : 0);
   s.threads = s.wpc * (s.hb + 1) * 32;
@@ -906,9 +1020,9 @@ static bool plan_smem(const Shape& s, SmemPlan& sm) {
 }
 
 int stream_supports(const PdDecodeArgs* a) {
-  if (a->io_dtype != PD_IO_F16) return PD_ERR_UNSUPPORTED;
-  if (a->kv_dtype == PD_KV_BF16) return PD_ERR_UNSUPPORTED;
-  const int eb = a->kv_dtype == PD_KV_F16 ? 2 : 1;
+  // bf16 pages go with bf16 q/out, every other page type with f16 q/out
+  if ((a->kv_dtype == PD_KV_BF16) != (a->io_dtype == PD_IO_BF16)) return PD_ERR_UNSUPPORTED;
+  const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   const int rowb = a->head_dim * eb;
   if (rowb != 128 && rowb != 256) return PD_ERR_UNSUPPORTED;
   if (a->batch <= 0) return PD_ERR_UNSUPPORTED;
@@ -940,7 +1054,7 @@ int stream_supports(const PdDecodeArgs* a) {
 }
 
 struct WorkspaceLayout {
-  uint64_t plan_off, lse_off, o_off, total;
+  uint64_t ticket_off, ticket_bytes, lse_off, o_off, total;
   int slots;
 };
 
@@ -948,8 +1062,9 @@ static WorkspaceLayout workspace_layout(const PdDecodeArgs* a, const Shape& s, i
   WorkspaceLayout w;
   const int group = a->num_q_heads / a->num_kv_heads;
   w.slots = sm_count * s.wpc + s.nvseq;
-  w.plan_off = 0;
-  w.lse_off = round_up64((uint64_t)(s.nvseq + 3) * 4, 256);
+  w.ticket_off = 0;
+  w.ticket_bytes = (uint64_t)a->batch * a->num_kv_heads * 4;
+  w.lse_off = round_up64(w.ticket_bytes, 256);
   w.o_off = w.lse_off + round_up64((uint64_t)w.slots * s.hb * group * 4, 256);
   w.total = w.o_off + round_up64((uint64_t)w.slots * s.hb * group * a->head_dim * 4, 256);
   return w;
@@ -1003,13 +1118,13 @@ static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
   }
   EncodeFn enc = encode_fn();
   if (!enc) return false;
-  const int eb = k.kv == PD_KV_F16 ? 2 : 1;
+  const int eb = is_16bit(k.kv) ? 2 : 1;
   const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
   const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
   const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMap m;
-  const CUresult r = enc(&m, eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+  const CUresult r = enc(&m, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
                          const_cast<void*>(k.base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1023,11 +1138,10 @@ static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
   return true;
 }
 
-template <int KV, int D, int HB, bool SCALED, int NG>
-static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                             int grid, uint32_t smem, cudaStream_t st) {
-  using C = StreamCfg<KV, D, HB, SCALED>;
-  auto* kern = stream_decode_kernel<KV, D, HB, SCALED, NG>;
+template <int KV, int D, int HB, bool SCALED, int NG, int WPC>
+static cudaError_t launch_wpc(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                              int grid, uint32_t smem, cudaStream_t st) {
+  auto* kern = stream_decode_kernel<KV, D, HB, SCALED, NG, WPC>;
   static bool configured[64] = {};  // per device: the opt-in shared-memory limit has been raised
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorInvalidDevice;
@@ -1036,8 +1150,17 @@ static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, cons
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kern<<<grid, C::THREADS, smem, st>>>(sp, mk, mv);
+  kern<<<grid, WPC * (HB + 1) * 32, smem, st>>>(sp, mk, mv);
   return cudaGetLastError();
+}
+
+template <int KV, int D, int HB, bool SCALED, int NG>
+static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
+                             int grid, uint32_t smem, cudaStream_t st) {
+  if constexpr (HB == 8 && !is_16bit(KV)) {
+    if (sp.wpc == 2) return launch_wpc<KV, D, HB, SCALED, NG, 2>(sp, mk, mv, grid, smem, st);
+  }
+  return launch_wpc<KV, D, HB, SCALED, NG, base_workers_per_cta(HB)>(sp, mk, mv, grid, smem, st);
 }
 
 // groups of up to 8 query heads fit one 8-wide n-tile, up to 16 need two
@@ -1057,22 +1180,6 @@ static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& 
     case 2: return launch_one<KV, D, 2, SCALED>(sp, mk, mv, grid, smem, st);
     default: return launch_one<KV, D, 1, SCALED>(sp, mk, mv, grid, smem, st);
   }
-}
-
-// Launches the slot merge behind the decode kernel with programmatic dependent launch, so its
-// launch latency overlaps the decode grid's tail.
-static cudaError_t launch_slot_merge(const MergeSlotsParams& mp, int rows, cudaStream_t st) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)rows);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, stream_merge_kernel, mp);
 }
 
 int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
@@ -1098,42 +1205,31 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   sp.nhb = s.nhb;
   sp.splits = s.splits;
   sp.nstage = sm.nstage;
+  sp.wpc = s.wpc;
   sp.bar_off = sm.bar_off;
   sp.meta_off = sm.meta_off;
   sp.misc_off = sm.misc_off;
   sp.prefix_off = sm.prefix_off;
-  sp.plan = (int32_t*)((char*)a->workspace + wl.plan_off);
+  sp.tickets = (int32_t*)((char*)a->workspace + wl.ticket_off);
   sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
 
   const cudaStream_t st = (cudaStream_t)a->stream;
+  // the arrival counters of the in-kernel merge start at zero
+  if (cudaMemsetAsync(sp.tickets, 0, wl.ticket_bytes, st) != cudaSuccess) return PD_ERR_CUDA;
   cudaError_t e;
   if (a->kv_dtype == PD_KV_F16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else if (a->kv_dtype == PD_KV_BF16) {
+    e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
     e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                  : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else {
     e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   }
-  if (e != cudaSuccess) return PD_ERR_CUDA;
-
-  MergeSlotsParams mp;
-  mp.plan = sp.plan;
-  mp.part_o = sp.p.part_o;
-  mp.part_lse = sp.p.part_lse;
-  mp.batch = a->batch;
-  mp.hq = a->num_q_heads;
-  mp.group = a->num_q_heads / a->num_kv_heads;
-  mp.hb_heads = s.hb;
-  mp.splits = s.splits;
-  mp.d = a->head_dim;
-  mp.out = a->out;
-  mp.o_sb = a->out_stride_b;
-  mp.o_sh = a->out_stride_h;
-  mp.res_o = a->result_f32;
-  mp.res_lse = a->result_lse;
-  return launch_slot_merge(mp, a->batch * a->num_q_heads, st) == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+  return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1168,12 +1264,12 @@ static void* static_scratch_address() {
 static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
   EncodeFn enc = encode_fn();
   if (!enc) return false;
-  const int eb = k.kv == PD_KV_F16 ? 2 : 1;
+  const int eb = is_16bit(k.kv) ? 2 : 1;
   const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
   const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
   const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return enc(out, eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+  return enc(out, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
              const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -1195,8 +1291,8 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   key.base = a->v_cache;
   if (!encode_tensor_map_in_place(key, &mv)) return PD_ERR_CUDA;
 
-  // Nothing in the scratch has to start at zero: the decode kernel writes the plan and every
-  // slot the plan names before the merge kernel, ordered after it on the stream, reads them.
+  // Only the arrival counters have to start at zero; they are cleared below, on the stream,
+  // before the kernel.  Every partial slot is written before the merge inside the kernel reads it.
   StreamParams sp;
   sp.p = p;
   sp.p.num_splits = s.splits;
@@ -1206,42 +1302,31 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   sp.nhb = s.nhb;
   sp.splits = s.splits;
   sp.nstage = sm.nstage;
+  sp.wpc = s.wpc;
   sp.bar_off = sm.bar_off;
   sp.meta_off = sm.meta_off;
   sp.misc_off = sm.misc_off;
   sp.prefix_off = sm.prefix_off;
-  sp.plan = (int32_t*)(scratch + wl.plan_off);
+  sp.tickets = (int32_t*)(scratch + wl.ticket_off);
   sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
 
   const cudaStream_t st = (cudaStream_t)a->stream;
+  // the arrival counters of the in-kernel merge start at zero
+  if (cudaMemsetAsync(sp.tickets, 0, wl.ticket_bytes, st) != cudaSuccess) return PD_ERR_CUDA;
   cudaError_t e;
   if (a->kv_dtype == PD_KV_F16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  } else if (a->kv_dtype == PD_KV_BF16) {
+    e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
     e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                  : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else {
     e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   }
-  if (e != cudaSuccess) return PD_ERR_CUDA;
-
-  MergeSlotsParams mp;
-  mp.plan = sp.plan;
-  mp.part_o = sp.p.part_o;
-  mp.part_lse = sp.p.part_lse;
-  mp.batch = a->batch;
-  mp.hq = a->num_q_heads;
-  mp.group = a->num_q_heads / a->num_kv_heads;
-  mp.hb_heads = s.hb;
-  mp.splits = s.splits;
-  mp.d = a->head_dim;
-  mp.out = a->out;
-  mp.o_sb = a->out_stride_b;
-  mp.o_sh = a->out_stride_h;
-  mp.res_o = a->result_f32;
-  mp.res_lse = a->result_lse;
-  return launch_slot_merge(mp, a->batch * a->num_q_heads, st) == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+  return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
 }  // namespace pd

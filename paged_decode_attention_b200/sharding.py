@@ -113,7 +113,7 @@ class KVRangeShardedDecoder:
         self.out = torch.empty_like(q)
         self.decode_fn = decode_fn or _cuda_decode
         self.merge_fn = merge_fn or _cuda_merge
-        self.launches_per_step = 3  # decode, its split merge, the cross-rank merge
+        self.launches_per_step = 2  # decode (merges its own splits), the cross-rank merge
 
     def step(self) -> torch.Tensor:
         b, hq, d = self.q.shape
