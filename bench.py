@@ -203,7 +203,10 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a rank that dies must not leave the others waiting for NCCL's ten-minute default
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=args.pg_timeout))
 
     w = synth.WORKLOADS[args.workload]
     kv_sharded = args.workload == "c4" and world > 1
@@ -275,8 +278,11 @@ def run_ours(args) -> None:
         t_wall = time.perf_counter() - t_wall0
         # keep the sampler alive long enough to see the GPU under load for short regions
         if t_wall < 0.5:
-            t_end = time.perf_counter() + 0.6
-            while time.perf_counter() < t_end:
+            # the same number of extra steps on every rank: a step may contain a collective
+            extra = torch.tensor([int(0.6 / max(t_wall / args.steps, 1e-6))], device=dev, dtype=torch.int64)
+            if world > 1:
+                dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+            for _ in range(min(int(extra.item()), 20000)):
                 step()
             torch.cuda.synchronize()
     per_step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
@@ -381,6 +387,7 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=40000,
                     help="size of the CPU sample in tokens")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--pg-timeout", type=int, default=120, help="process-group timeout in seconds")
     ap.add_argument("--graph-steps", type=int, default=0,
                     help="also time this many steps per CUDA-graph replay (GPU time without host gaps)")
     args = ap.parse_args()
