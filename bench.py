@@ -34,6 +34,11 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "decode_attn_hbm_gbs"
+# DRAM bytes moved per algorithmic byte, from one ncu capture of the streaming kernel per
+# workload shape (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic KV bytes of
+# the captured case; see profiles/).  Traffic grows in proportion to the tokens processed, so
+# the ratio scales a full launch.
+NCU_TRAFFIC_RATIO = {"c2": 1.013, "c3": 1.020}
 L2_BYTES = 126 << 20
 FALLBACK_HBM_GBS = 6650.0
 
@@ -349,8 +354,11 @@ def run_ours(args) -> None:
                                    else f"request sharding x{world}, no communication")},
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu_gbs / peak, "peak_kind": f"of {peak_kind}",
-                     "traffic": None,
-                     "note": "algorithmic KV bytes of rank 0 / mean step time (decode + merge kernels)"},
+                     "traffic": (my_bytes * NCU_TRAFFIC_RATIO[args.workload]
+                                 if args.workload in NCU_TRAFFIC_RATIO and not args.batch else None),
+                     "note": "achieved = algorithmic KV bytes of rank 0 / mean step time (memset + the one "
+                             "decode launch); traffic = DRAM bytes per launch, scaled from the ncu "
+                             "capture of a smaller batch of the same shape (profiles/)"},
         "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),

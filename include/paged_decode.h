@@ -156,6 +156,27 @@ typedef struct PdGatherArgs {
   int32_t s_max;
 } PdGatherArgs;
 
+/* Arguments of the cache write.  Replaces the call of vLLM's reshape_and_cache_flash in the
+ * reference's backend (integration/vllm_backend.py:117-122) and, for 8-bit caches, the
+ * quantisation rule of quantize_kv (pagedattn/cache.py:33-48) that the reference applies only
+ * when it builds fixtures. */
+typedef struct PdCacheWriteArgs {
+  const void* key;   /* [num_tokens, num_kv_heads, head_dim] io_dtype, head_dim contiguous */
+  const void* value;
+  int64_t in_stride_token, in_stride_head;
+  void* k_cache;     /* NHD pages, kv_dtype elements */
+  void* v_cache;
+  int64_t kv_stride_block, kv_stride_token, kv_stride_head;
+  void* k_scale;     /* fp16 [num_blocks, block_size, num_kv_heads]; required for PD_KV_I8 */
+  void* v_scale;
+  int64_t scale_stride_block, scale_stride_token;
+  const int64_t* slot_mapping; /* [num_tokens] block * block_size + offset; negative = skip */
+  int32_t num_tokens, num_kv_heads, head_dim, block_size, num_blocks;
+  int32_t kv_dtype, io_dtype;
+  uint32_t* status;  /* optional, PD_DEV_BAD_BLOCK for a slot outside the pool */
+  void* stream;
+} PdCacheWriteArgs;
+
 /* ABI version of the loaded library (PD_ABI_VERSION it was built with). */
 PD_API int pd_abi_version(void);
 
@@ -192,6 +213,10 @@ PD_API int pd_merge(const PdMergeArgs* args);
 
 /* Dense dequantised fp16 gather (see PdGatherArgs). */
 PD_API int pd_gather(const PdGatherArgs* args);
+
+/* Stores this step's keys and values into their cache slots, quantising to the cache's
+ * element type with the reference's rules, bit for bit (see PdCacheWriteArgs). */
+PD_API int pd_cache_write(const PdCacheWriteArgs* args);
 
 /*
  * pd_decode for callers that have no scratch memory to give and may not allocate any.  It has

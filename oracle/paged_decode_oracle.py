@@ -93,6 +93,40 @@ def quantize_int8(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
     return q, scale[..., 0]
 
 
+def quantize_e5m2(x: np.ndarray) -> np.ndarray:
+    """fp16 -> fp8_e5m2 bits, round to nearest even on the fp16 bits: what the reference's
+    ``x.to(torch.float8_e5m2)`` does for finite inputs (pagedattn/cache.py:41-42)."""
+    h = x.astype(np.float16).view(np.uint16).astype(np.uint32)
+    return ((h + 0x7F + ((h >> 8) & 1)) >> 8).astype(np.uint8)
+
+
+def cache_write(key: np.ndarray, value: np.ndarray, cache: OracleCache, slot_mapping: np.ndarray) -> None:
+    """Store fp16 rows key/value [T, Hkv, D] at slot_mapping[t] = block * PAGE + offset, in place.
+
+    The scatter the reference's backend delegates to the engine
+    (integration/vllm_backend.py:117-122) combined with quantize_kv's rule per cache dtype
+    (pagedattn/cache.py:33-48).  Negative slots are padding and are skipped.
+    """
+    for t, slot in enumerate(np.asarray(slot_mapping).tolist()):
+        if slot < 0:
+            continue
+        blk, off = divmod(int(slot), cache.block_size)
+        for store, scale, x in ((cache.k_cache, cache.k_scale, key[t]), (cache.v_cache, cache.v_scale, value[t])):
+            if cache.kv_dtype == "fp16":
+                store[blk, off] = x.astype(np.float16)
+            elif cache.kv_dtype == "bf16":
+                u = x.astype(np.float32).view(np.uint32)
+                store[blk, off] = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+            elif cache.kv_dtype == "fp8_e5m2":
+                store[blk, off] = quantize_e5m2(x)
+                if scale is not None:
+                    scale[blk, off] = np.float16(1.0)
+            else:
+                q, sc = quantize_int8(x)
+                store[blk, off] = q
+                scale[blk, off] = sc
+
+
 def gather_contiguous(cache: OracleCache) -> tuple[np.ndarray, np.ndarray]:
     """Dense [B, Hkv, S_max, D] fp16 K and V (pagedattn/cache.py:187-215).
 

@@ -66,6 +66,20 @@ class PdMergeArgs(ctypes.Structure):
     ]
 
 
+class PdCacheWriteArgs(ctypes.Structure):
+    _fields_ = [
+        ("key", _c_vp), ("value", _c_vp), ("in_stride_token", _c_i64), ("in_stride_head", _c_i64),
+        ("k_cache", _c_vp), ("v_cache", _c_vp),
+        ("kv_stride_block", _c_i64), ("kv_stride_token", _c_i64), ("kv_stride_head", _c_i64),
+        ("k_scale", _c_vp), ("v_scale", _c_vp),
+        ("scale_stride_block", _c_i64), ("scale_stride_token", _c_i64),
+        ("slot_mapping", _c_vp),
+        ("num_tokens", _c_i32), ("num_kv_heads", _c_i32), ("head_dim", _c_i32),
+        ("block_size", _c_i32), ("num_blocks", _c_i32), ("kv_dtype", _c_i32), ("io_dtype", _c_i32),
+        ("status", _c_vp), ("stream", _c_vp),
+    ]
+
+
 class PdGatherArgs(ctypes.Structure):
     _fields_ = [("cache", ctypes.POINTER(PdDecodeArgs)), ("k_dense", _c_vp), ("v_dense", _c_vp),
                 ("s_max", _c_i32)]
@@ -73,7 +87,7 @@ class PdGatherArgs(ctypes.Structure):
 
 EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
            "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather",
-           "pd_decode_static")
+           "pd_decode_static", "pd_cache_write")
 
 STATIC_SCRATCH_BYTES = 8 << 20
 ERR_TOO_LARGE = -5
@@ -116,6 +130,8 @@ def load() -> ctypes.CDLL:
     lib.pd_merge.argtypes = [ctypes.POINTER(PdMergeArgs)]
     lib.pd_gather.restype = ctypes.c_int
     lib.pd_gather.argtypes = [ctypes.POINTER(PdGatherArgs)]
+    lib.pd_cache_write.restype = ctypes.c_int
+    lib.pd_cache_write.argtypes = [ctypes.POINTER(PdCacheWriteArgs)]
     _lib = lib
     return lib
 

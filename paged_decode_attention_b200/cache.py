@@ -203,3 +203,46 @@ def gather_contiguous(cache: PagedKVCache) -> tuple[torch.Tensor, torch.Tensor]:
     if cache.batch and s_max:
         _cabi.gather(cache, k, v, s_max)
     return k, v
+
+
+def cache_write(key: torch.Tensor, value: torch.Tensor, cache: PagedKVCache, slot_mapping: torch.Tensor,
+                status: torch.Tensor | None = None) -> None:
+    """Store this step's keys and values (``[num_tokens, H_kv, D]``) into their cache slots.
+
+    ``slot_mapping[t] = block * block_size + offset`` (int64, negative = padding, skipped).
+    Quantises to the cache dtype on the way with ``quantize_kv``'s rules, bit for bit,
+    including the per-(token, head) int8 scales.  It stands where the reference's backend
+    calls the engine's ``reshape_and_cache_flash`` (``integration/vllm_backend.py:117-122``),
+    and is the producer of exactly the layout the decode kernels read.
+    """
+    import ctypes
+
+    from . import _cabi
+    from .config import KV_CODE
+
+    if not key.is_cuda:
+        raise _cabi.NativeLibraryError("cache_write runs on CUDA tensors only")
+    if key.shape != value.shape or key.dim() != 3 or key.stride() != value.stride() or key.stride(2) != 1:
+        raise ValueError("key and value must be alike [num_tokens, H_kv, D] with head_dim contiguous")
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous int64 tensor")
+    if slot_mapping.numel() < key.shape[0]:
+        raise ValueError("slot_mapping is shorter than the token count")
+    k = cache.k_cache
+    a = _cabi.PdCacheWriteArgs()
+    a.key, a.value = key.data_ptr(), value.data_ptr()
+    a.in_stride_token, a.in_stride_head = key.stride(0), key.stride(1)
+    a.k_cache, a.v_cache = k.data_ptr(), cache.v_cache.data_ptr()
+    a.kv_stride_block, a.kv_stride_token, a.kv_stride_head = k.stride(0), k.stride(1), k.stride(2)
+    if cache.k_scale is not None:
+        a.k_scale, a.v_scale = cache.k_scale.data_ptr(), cache.v_scale.data_ptr()
+        a.scale_stride_block, a.scale_stride_token = cache.k_scale.stride(0), cache.k_scale.stride(1)
+    a.slot_mapping = slot_mapping.data_ptr()
+    a.num_tokens, a.num_kv_heads, a.head_dim = int(key.shape[0]), int(key.shape[1]), int(key.shape[2])
+    a.block_size, a.num_blocks = int(k.shape[1]), int(k.shape[0])
+    a.kv_dtype, a.io_dtype = KV_CODE[cache.kv_dtype], _cabi.IO_CODE[key.dtype]
+    if status is not None:
+        a.status = status.data_ptr()
+    a.stream = torch.cuda.current_stream(key.device).cuda_stream
+    with torch.cuda.device(key.device):
+        _cabi.check(_cabi.load().pd_cache_write(ctypes.byref(a)), "pd_cache_write")

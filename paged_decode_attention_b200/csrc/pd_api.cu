@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "pd_common.cuh"
+#include "pd_cache_write.cuh"
 #include "pd_merge.cuh"
 #include "pd_simple.cuh"
 #include "pd_stream.h"
@@ -370,6 +371,67 @@ int pd_gather(const PdGatherArgs* g) {
     default: PD_GATHER(PD_KV_I8, true) break;
   }
 #undef PD_GATHER
+  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
+
+int pd_cache_write(const PdCacheWriteArgs* a) {
+  if (!a || !a->key || !a->value || !a->k_cache || !a->v_cache || !a->slot_mapping)
+    return PD_ERR_INVALID_ARG;
+  if (a->num_tokens < 0 || a->num_kv_heads <= 0 || a->block_size <= 0 || a->num_blocks <= 0)
+    return PD_ERR_INVALID_ARG;
+  if (a->kv_dtype < PD_KV_F16 || a->kv_dtype > PD_KV_I8) return PD_ERR_INVALID_ARG;
+  if (a->io_dtype != PD_IO_F16 && a->io_dtype != PD_IO_BF16) return PD_ERR_INVALID_ARG;
+  if ((a->k_scale == nullptr) != (a->v_scale == nullptr)) return PD_ERR_INVALID_ARG;
+  if (a->kv_dtype == PD_KV_I8 && !a->k_scale) return PD_ERR_INVALID_ARG;
+  if (a->head_dim != 32 && a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256)
+    return PD_ERR_UNSUPPORTED;
+  // the reference quantises fp16 inputs; 8-bit caches therefore take fp16 keys and values
+  if ((a->kv_dtype == PD_KV_I8 || a->kv_dtype == PD_KV_E5M2) && a->io_dtype != PD_IO_F16)
+    return PD_ERR_UNSUPPORTED;
+  if (a->num_tokens == 0) return PD_OK;
+  CacheWriteParams p;
+  p.key = a->key;
+  p.value = a->value;
+  p.in_st = a->in_stride_token;
+  p.in_sh = a->in_stride_head;
+  p.k_cache = a->k_cache;
+  p.v_cache = a->v_cache;
+  p.kv_sb = a->kv_stride_block;
+  p.kv_st = a->kv_stride_token;
+  p.kv_sh = a->kv_stride_head;
+  p.k_scale = (__half*)a->k_scale;
+  p.v_scale = (__half*)a->v_scale;
+  p.sc_sb = a->scale_stride_block;
+  p.sc_st = a->scale_stride_token;
+  p.slot_mapping = a->slot_mapping;
+  p.num_tokens = a->num_tokens;
+  p.hkv = a->num_kv_heads;
+  p.d = a->head_dim;
+  p.page = a->block_size;
+  p.num_blocks = a->num_blocks;
+  p.status = a->status;
+  const int64_t rows = (int64_t)a->num_tokens * a->num_kv_heads;
+  const unsigned blocks = (unsigned)((rows + 3) / 4);
+  const cudaStream_t st = (cudaStream_t)a->stream;
+  const bool bf = a->io_dtype == PD_IO_BF16;
+#define PD_CW_D(KV, BF)                                                              \
+  switch (a->head_dim) {                                                             \
+    case 32: cache_write_kernel<KV, 32, BF><<<blocks, 128, 0, st>>>(p); break;       \
+    case 64: cache_write_kernel<KV, 64, BF><<<blocks, 128, 0, st>>>(p); break;       \
+    case 128: cache_write_kernel<KV, 128, BF><<<blocks, 128, 0, st>>>(p); break;     \
+    default: cache_write_kernel<KV, 256, BF><<<blocks, 128, 0, st>>>(p); break;      \
+  }
+  switch (a->kv_dtype) {
+    case PD_KV_F16:
+      if (bf) { PD_CW_D(PD_KV_F16, true) } else { PD_CW_D(PD_KV_F16, false) }
+      break;
+    case PD_KV_BF16:
+      if (bf) { PD_CW_D(PD_KV_BF16, true) } else { PD_CW_D(PD_KV_BF16, false) }
+      break;
+    case PD_KV_E5M2: PD_CW_D(PD_KV_E5M2, false) break;
+    default: PD_CW_D(PD_KV_I8, false) break;
+  }
+#undef PD_CW_D
   return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 

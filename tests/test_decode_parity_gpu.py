@@ -218,3 +218,68 @@ def test_rejects_bad_arguments_without_launching():
         pda.paged_decode(q[:, :, :64], cache)
     args = pdec.build_args(q, cache, torch.empty_like(q), num_splits=4, kernel="simple")
     assert _cabi.load().pd_decode(ctypes.byref(args)) == -3  # split scratch not supplied
+
+
+@pytest.mark.parametrize("kv_dtype", ["fp16", "bf16", "fp8_e5m2", "int8"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_cache_write_is_bit_exact_and_feeds_decode(kv_dtype, d):
+    """The cache-write kernel stores what the reference's quantize_kv would, bit for bit, and a
+    decode over the pages it wrote equals the oracle's decode over the oracle's pages."""
+    rng = np.random.Generator(np.random.PCG64(1234 + d))
+    hq, hkv, page, nb = 16, 4, 16, 12
+    lens = np.array([37, 90], dtype=np.int32)
+    table = rng.permutation(nb).astype(np.int32).reshape(2, 6)
+    store = {"fp16": np.float16, "bf16": np.uint16, "fp8_e5m2": np.uint8, "int8": np.int8}[kv_dtype]
+    scaled = kv_dtype == "int8"
+    oc = po.OracleCache(hq, hkv, d, page, kv_dtype, np.zeros((nb, page, hkv, d), store),
+                        np.zeros((nb, page, hkv, d), store),
+                        np.zeros((nb, page, hkv), np.float16) if scaled else None,
+                        np.zeros((nb, page, hkv), np.float16) if scaled else None, table, lens)
+    cache = helpers.to_device_cache(oc)
+    tokens = int(lens.sum())
+    key = (rng.standard_normal((tokens + 2, hkv, d), dtype=np.float32) * 1.5).astype(np.float16)
+    val = rng.standard_normal((tokens + 2, hkv, d), dtype=np.float32).astype(np.float16)
+    key[3, 1] = 0  # an all-zero row
+    slots = np.concatenate([table[b, np.arange(n) // page].astype(np.int64) * page + np.arange(n) % page
+                            for b, n in enumerate(lens)] + [np.array([-1, -1], dtype=np.int64)])
+    po.cache_write(key, val, oc, slots)
+    io = torch.bfloat16 if kv_dtype == "bf16" else torch.float16
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pda.cache_write(torch.from_numpy(key).cuda().to(io), torch.from_numpy(val).cuda().to(io), cache,
+                    torch.from_numpy(slots).cuda(), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got = adapters_from(cache)
+    if kv_dtype == "bf16":
+        # the device input was rounded to bf16 first; compare against the same rounding
+        oc2 = po.OracleCache(hq, hkv, d, page, kv_dtype, np.zeros_like(oc.k_cache), np.zeros_like(oc.v_cache),
+                             None, None, table, lens)
+        po.cache_write(key, val, oc2, slots)
+        oc = oc2
+    assert np.array_equal(got.k_cache.view(np.uint8), oc.k_cache.view(np.uint8))
+    assert np.array_equal(got.v_cache.view(np.uint8), oc.v_cache.view(np.uint8))
+    if scaled:
+        assert np.array_equal(got.k_scale.view(np.uint16), oc.k_scale.view(np.uint16))
+        assert np.array_equal(got.v_scale.view(np.uint16), oc.v_scale.view(np.uint16))
+    q_np = rng.standard_normal((2, hq, d), dtype=np.float32).astype(np.float16)
+    ref = c_oracle.decode(q_np.astype(np.float32), oc)
+    out = pda.paged_decode(torch.from_numpy(q_np).cuda().to(io), cache)
+    helpers.assert_close(out, ref, bf16=kv_dtype == "bf16", what=f"decode after write {kv_dtype}")
+
+
+def adapters_from(cache):
+    from oracle import adapters
+
+    return adapters.from_torch_cache(cache)
+
+
+def test_cache_write_flags_slots_outside_the_pool():
+    oc = po.OracleCache(4, 2, 64, 16, "fp16", np.zeros((2, 16, 2, 64), np.float16), np.zeros((2, 16, 2, 64), np.float16),
+                        None, None, np.zeros((1, 2), np.int32), np.zeros(1, np.int32))
+    cache = helpers.to_device_cache(oc)
+    kv = torch.ones((3, 2, 64), dtype=torch.float16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pda.cache_write(kv, kv, cache, torch.tensor([5, 2 * 16 + 1, -1], device="cuda"), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & _cabi.DEV_BAD_BLOCK
+    assert float(cache.k_cache[0, 5].min()) == 1.0 and float(cache.k_cache.sum()) == 2 * 64

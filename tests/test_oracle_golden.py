@@ -75,6 +75,7 @@ def test_quantize_dequantize_known_answers(golden):
     assert np.array_equal(deq.view(np.uint16), golden["quant/int8_dequant"].view(np.uint16))
     bits = cases._f16_to_e5m2_bits(x)
     assert np.array_equal(bits, golden["quant/e5m2_bits"])
+    assert np.array_equal(po.quantize_e5m2(x), golden["quant/e5m2_bits"])
     deq8 = po.dequantize_kv(bits, None, "fp8_e5m2")
     assert np.array_equal(deq8.view(np.uint16), golden["quant/e5m2_dequant"].view(np.uint16))
 
@@ -115,3 +116,26 @@ def test_numpy_and_c_partials_agree():
     o2, l2 = c_oracle.decode(q.astype(np.float32), oc, lo=lo, hi=hi, want_lse=True)
     assert _rel(o1, o2) < ORACLE_REL
     assert np.allclose(l1, l2, rtol=0, atol=2e-5)
+
+
+def test_oracle_cache_write_reproduces_quantize_kv(golden):
+    """Rows scattered by the oracle's cache write hold exactly the reference's quantize_kv output."""
+    x = golden["quant/x"]  # [37, 4, 64] fp16
+    slots = np.random.Generator(np.random.PCG64(5)).permutation(48)[:37].astype(np.int64)
+    slots[5] = -1
+    for kv_dtype, want, want_scale in (("int8", golden["quant/int8"], golden["quant/int8_scale"]),
+                                       ("fp8_e5m2", golden["quant/e5m2_bits"], None)):
+        store = np.int8 if kv_dtype == "int8" else np.uint8
+        oc = po.OracleCache(8, 4, 64, 16, kv_dtype, np.zeros((3, 16, 4, 64), store), np.zeros((3, 16, 4, 64), store),
+                            np.zeros((3, 16, 4), np.float16) if want_scale is not None else None,
+                            np.zeros((3, 16, 4), np.float16) if want_scale is not None else None,
+                            np.zeros((1, 3), np.int32), np.zeros(1, np.int32))
+        po.cache_write(x, x[::-1].copy(), oc, slots)
+        for t, slot in enumerate(slots):
+            if slot < 0:
+                continue
+            blk, off = divmod(int(slot), 16)
+            assert np.array_equal(oc.k_cache[blk, off], want[t])
+            assert np.array_equal(oc.v_cache[blk, off], want[36 - t])
+            if want_scale is not None:
+                assert np.array_equal(oc.k_scale[blk, off].view(np.uint16), want_scale[t].view(np.uint16))
