@@ -218,6 +218,10 @@ def run_ours(args) -> None:
     if kv_sharded:
         q, cache = sharding.make_kv_range_shard(args.workload, rank, world, dev, seed=args.seed)
         runner = sharding.KVRangeShardedDecoder(q, cache, group=dist.group.WORLD, kernel=args.kernel)
+        for _ in range(2):
+            runner.step()
+        if not args.no_graph:
+            runner.capture()  # decode + all-gather + merge replayed as one CUDA graph
         step = runner.step
         launches_per_step = runner.launches_per_step
     else:
@@ -395,6 +399,8 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=40000,
                     help="size of the CPU sample in tokens")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="KV-range-sharded runs: issue the step from the host instead of a CUDA graph")
     ap.add_argument("--pg-timeout", type=int, default=120, help="process-group timeout in seconds")
     ap.add_argument("--graph-steps", type=int, default=0,
                     help="also time this many steps per CUDA-graph replay (GPU time without host gaps)")

@@ -301,6 +301,35 @@ def merge_partials(part_out: torch.Tensor, part_lse: torch.Tensor, out: torch.Te
     return (out, f32, lse) if want_f32 else out
 
 
+class MergeStep:
+    """``merge_partials`` prepared once for fixed buffers (see ``DecodeStep``)."""
+
+    def __init__(self, part_out: torch.Tensor, part_lse: torch.Tensor, out: torch.Tensor):
+        if not part_out.is_cuda:
+            raise _cabi.NativeLibraryError("MergeStep runs on CUDA tensors only")
+        p, b, hq, d = part_out.shape
+        if not (part_out[0].is_contiguous() and part_lse[0].is_contiguous() and out.is_contiguous()):
+            raise ValueError("each partial, each lse block and out must be dense")
+        self._keep = (part_out, part_lse, out)
+        self.out, self.device = out, part_out.device
+        m = _cabi.PdMergeArgs()
+        m.part_out, m.part_lse = part_out.data_ptr(), part_lse.data_ptr()
+        m.out_stride_p, m.out_stride_row = part_out.stride(0), d
+        m.lse_stride_p, m.lse_stride_row = part_lse.stride(0), 1
+        m.num_parts, m.num_rows, m.head_dim = p, b * hq, d
+        m.out, m.dst_stride_row, m.io_dtype = out.data_ptr(), d, _cabi.IO_CODE[out.dtype]
+        self.args, self._ref, self._fn = m, ctypes.byref(m), _cabi.load().pd_merge
+
+    def step(self) -> torch.Tensor:
+        self.args.stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = _call_on_device(self.device, self._fn, self._ref)
+        if rc != 0:
+            _cabi.check(rc, "pd_merge")
+        return self.out
+
+    __call__ = step
+
+
 class HostDecoder:
     """Decode steps for callers whose q, block table, lengths and result live in host memory.
 

@@ -78,19 +78,6 @@ def make_kv_range_shard(name: str, rank: int, world: int, device, seed: int = 0,
     return q, cache
 
 
-def _cuda_decode(q: torch.Tensor, cache: PagedKVCache, f32: torch.Tensor, lse: torch.Tensor,
-                 kernel: str) -> None:
-    from .decode import paged_decode
-
-    paged_decode(q, cache, result_f32=f32, result_lse=lse, kernel=kernel)
-
-
-def _cuda_merge(parts: torch.Tensor, lses: torch.Tensor, out: torch.Tensor) -> None:
-    from .decode import merge_partials
-
-    merge_partials(parts, lses, out=out)
-
-
 class KVRangeShardedDecoder:
     """Decode step of one rank of a KV-range-sharded group.
 
@@ -110,19 +97,49 @@ class KVRangeShardedDecoder:
         self.f32 = self.local[: self.n_o].view(b, hq, d)
         self.lse = self.local[self.n_o:].view(b, hq)
         self.gathered = torch.empty((self.world, self.local.numel()), dtype=torch.float32, device=q.device)
+        self.parts = self.gathered[:, : self.n_o].view(self.world, b, hq, d)
+        self.lses = self.gathered[:, self.n_o:].view(self.world, b, hq)
         self.out = torch.empty_like(q)
-        self.decode_fn = decode_fn or _cuda_decode
-        self.merge_fn = merge_fn or _cuda_merge
+        self.graph = None
+        if decode_fn is None:
+            from .decode import DecodeStep, MergeStep
+
+            decode_step = DecodeStep(q, cache, None, result_f32=self.f32, result_lse=self.lse, kernel=kernel)
+            merge_step = MergeStep(self.parts, self.lses, self.out)
+            decode_fn = lambda *_: decode_step.step()
+            merge_fn = lambda *_: merge_step.step()
+        self.decode_fn, self.merge_fn = decode_fn, merge_fn
         self.launches_per_step = 2  # decode (merges its own splits), the cross-rank merge
 
-    def step(self) -> torch.Tensor:
-        b, hq, d = self.q.shape
+    def _run(self) -> None:
         self.decode_fn(self.q, self.cache, self.f32, self.lse, self.kernel)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered.view(-1), self.local, group=self.group)
         else:
             self.gathered[0].copy_(self.local)
-        parts = self.gathered[:, : self.n_o].view(self.world, b, hq, d)
-        lses = self.gathered[:, self.n_o:].view(self.world, b, hq)
-        self.merge_fn(parts, lses, self.out)
+        self.merge_fn(self.parts, self.lses, self.out)
+
+    def capture(self) -> None:
+        """Record decode -> all-gather -> merge into one CUDA graph; ``step`` then replays it.
+
+        At eight ranks a rank's slice of a long request decodes in a few tens of
+        microseconds, less than the host needs to issue the three operations; replaying a
+        graph takes the host out of the step.  Every rank of the group must call this at the
+        same point (the all-gather is captured collectively), after at least one plain step.
+        """
+        side = torch.cuda.Stream(device=self.q.device)
+        side.wait_stream(torch.cuda.current_stream(self.q.device))
+        with torch.cuda.stream(side):
+            self._run()
+        torch.cuda.current_stream(self.q.device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._run()
+        self.graph = graph
+
+    def step(self) -> torch.Tensor:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._run()
         return self.out

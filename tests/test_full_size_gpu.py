@@ -103,3 +103,16 @@ def test_prepared_step_equals_direct_call():
     step = pda.DecodeStep(q, cache)
     assert torch.equal(step.step(), pda.paged_decode(q, cache))
     assert torch.equal(step(), step.out)
+
+
+def test_sharded_decoder_single_rank_with_and_without_graph():
+    """The KV-range-sharded step degenerates to a plain decode on one rank; its CUDA-graph
+    replay must give the same bits as issuing the three operations from the host."""
+    q, cache = synth.make("c4", device="cuda", seed=6, seq_len=4096)
+    want = pda.paged_decode(q, cache)
+    dec = sharding.KVRangeShardedDecoder(q, cache)
+    plain = dec.step().clone()
+    assert float((plain.float() - want.float()).abs().max()) <= 1e-3
+    dec.capture()
+    dec.out.zero_()
+    assert torch.equal(dec.step(), plain)
