@@ -50,6 +50,7 @@ constexpr int kTileTokens = 16;
 __host__ __device__ constexpr bool is_16bit(int kv) { return kv == PD_KV_F16 || kv == PD_KV_BF16; }
 constexpr int kMaxVseq = 4096;
 constexpr int kMinTilesPerWorker = 4;
+constexpr int kMergeRadix = 8;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxStages = 12;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
@@ -538,7 +539,22 @@ __device__ __forceinline__ void for_each_segment(const int* prefix, int per, int
 template <int KV, int D>
 __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, int per, int v0,
                                            int splits, int hg, int head_in_block, int b, int kvh,
-                                           int lane) {
+                                           int lane, int rslot0 = 0, int rn = 0, int rstride = 1,
+                                           int dst_slot = -1) {
+  // Default: merge every segment the schedule gives the unit and write the final rows.  With
+  // rn > 0 the inputs are instead the rn slots rslot0, rslot0 + rstride, ...; with dst_slot >= 0
+  // the result goes back into that slot as a normalised partial (first level of a deep merge).
+  auto for_ranges = [&](auto&& f) {
+    if (rn > 0) {
+      f(rslot0, rn, rstride);
+      return;
+    }
+    for (int s = 0; s < splits; ++s) {
+      const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
+      if (last <= first) continue;
+      f(first / per + v0 + s, (last - 1) / per - first / per + 1, 1);
+    }
+  };
   constexpr int J = D / 16;
   constexpr unsigned kFull = 0xffffffffu;
   const int q = lane >> 2, c = lane & 3;
@@ -551,32 +567,26 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
     const bool live = row < p.group;
     const int64_t local = (int64_t)head_in_block * p.group + (live ? row : 0);
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) {
-      const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
-      if (last <= first) continue;
-      const int slot0 = first / per + v0 + s, n = (last - 1) / per - first / per + 1;
+    for_ranges([&](int slot0, int n, int stride) {
       const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
 #pragma unroll 4
-      for (int i = phase; i < n; i += sp_n) m = fmaxf(m, __ldcg(lp + (int64_t)i * hg));
-    }
+      for (int i = phase; i < n; i += sp_n) m = fmaxf(m, __ldcg(lp + (int64_t)i * stride * hg));
+    });
     for (int sh = 4 * rp; sh < 32; sh <<= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, sh));
     float denom = 0.f;
     float acc[J][4];
 #pragma unroll
     for (int j = 0; j < J; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     if (m > -INFINITY) {
-      for (int s = 0; s < splits; ++s) {
-        const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
-        if (last <= first) continue;
-        const int slot0 = first / per + v0 + s, n = (last - 1) / per - first / per + 1;
+      for_ranges([&](int slot0, int n, int stride) {
         const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
         const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
 #pragma unroll 2
         for (int i = phase; i < n; i += sp_n) {
-          const float lse = __ldcg(lp + (int64_t)i * hg);
+          const float lse = __ldcg(lp + (int64_t)i * stride * hg);
           float4 x[J];
 #pragma unroll
-          for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * hg * (D / 4) + 4 * j);
+          for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * stride * hg * (D / 4) + 4 * j);
           const float wgt = lse > -INFINITY ? exp2f(lse - m) : 0.f;
           denom += wgt;
 #pragma unroll
@@ -587,7 +597,7 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
             acc[j][3] = fmaf(wgt, x[j].w, acc[j][3]);
           }
         }
-      }
+      });
     }
     for (int sh = 4 * rp; sh < 32; sh <<= 1) {
       denom += __shfl_xor_sync(kFull, denom, sh);
@@ -599,6 +609,16 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
     }
     if (!live || phase != 0) continue;
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    if (dst_slot >= 0) {
+      // first level of a deep merge: the chunk's result replaces the partial in its first slot
+      const int64_t sr = (int64_t)dst_slot * hg + local;
+#pragma unroll
+      for (int j = 0; j < J; ++j)
+        *reinterpret_cast<float4*>(p.part_o + sr * D + 16 * j + 4 * c) =
+            make_float4(acc[j][0] * inv, acc[j][1] * inv, acc[j][2] * inv, acc[j][3] * inv);
+      if (c == 0) p.part_lse[sr] = denom > 0.f ? m + log2f(denom) : -INFINITY;
+      continue;
+    }
     const int hq = kvh * p.group + row;
     __half* dst16 = p.out ? (__half*)p.out + (int64_t)b * p.o_sb + (int64_t)hq * p.o_sh : nullptr;
     float* dst32 = p.res_o ? p.res_o + ((int64_t)b * p.hq + hq) * D : nullptr;
@@ -944,19 +964,57 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
       // whoever completes the count merges them all.  Nobody waits for anybody.
       __threadfence();
       __syncwarp();
-      int last = 0;
       const int v0 = (vi.hb * p.batch + vi.b) * sp.splits;
-      if (lane == 0) {
-        int expected = 0;
-        for_each_segment(prefix, per, v0, sp.splits, [&](int) { ++expected; });
-        int* ticket = sp.tickets + (int64_t)vi.b * p.hkv + kvh;
-        last = atomicAdd(ticket, 1) + 1 == expected;
-        if (last) *ticket = 0;  // leave the counter as it was found
+      int* unit_ticket = sp.tickets + (int64_t)vi.b * p.hkv + kvh;
+      // An unsplit request cut over more than kMergeRadix workers (one long request can span
+      // every worker) is merged in two levels: chunks of kMergeRadix consecutive segments
+      // first, each by the warp that completes the chunk, into the chunk's first slot; then
+      // the chunk results by the warp that completes the unit.  The chunk merges of one
+      // request run on different SMs at the same time.
+      int wfirst = 0, nseg = 0;
+      if (sp.splits == 1) {
+        wfirst = prefix[v0] / per;
+        nseg = (prefix[v0 + 1] - 1) / per - wfirst + 1;
       }
-      last = __shfl_sync(kFull, last, 0);
-      if (last) {
-        __threadfence();
-        merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane);
+      if (nseg > kMergeRadix) {
+        const int chunk = (w - wfirst) / kMergeRadix;
+        const int csize = min(kMergeRadix, nseg - chunk * kMergeRadix);
+        const int nchunk = (nseg + kMergeRadix - 1) / kMergeRadix;
+        const int cslot = wfirst + chunk * kMergeRadix + v0;
+        int done = 0;
+        if (lane == 0) {
+          int* chunk_ticket = sp.tickets + (int64_t)p.batch * p.hkv + (int64_t)cslot * HB + role;
+          done = atomicAdd(chunk_ticket, 1) + 1 == csize;
+          if (done) *chunk_ticket = 0;
+        }
+        if (__shfl_sync(kFull, done, 0)) {
+          __threadfence();
+          merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, cslot, csize, 1, cslot);
+          __threadfence();
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) {
+            last = atomicAdd(unit_ticket, 1) + 1 == nchunk;
+            if (last) *unit_ticket = 0;
+          }
+          if (__shfl_sync(kFull, last, 0)) {
+            __threadfence();
+            merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
+                              kMergeRadix, -1);
+          }
+        }
+      } else {
+        int last = 0;
+        if (lane == 0) {
+          int expected = 0;
+          for_each_segment(prefix, per, v0, sp.splits, [&](int) { ++expected; });
+          last = atomicAdd(unit_ticket, 1) + 1 == expected;
+          if (last) *unit_ticket = 0;  // leave the counter as it was found
+        }
+        if (__shfl_sync(kFull, last, 0)) {
+          __threadfence();
+          merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane);
+        }
       }
     }
     ++v;
@@ -1063,7 +1121,9 @@ static WorkspaceLayout workspace_layout(const PdDecodeArgs* a, const Shape& s, i
   const int group = a->num_q_heads / a->num_kv_heads;
   w.slots = sm_count * s.wpc + s.nvseq;
   w.ticket_off = 0;
-  w.ticket_bytes = (uint64_t)a->batch * a->num_kv_heads * 4;
+  // one counter per (request, kv head), then one per (slot, kv head of the block) for the
+  // chunks of deep merges
+  w.ticket_bytes = ((uint64_t)a->batch * a->num_kv_heads + (uint64_t)w.slots * s.hb) * 4;
   w.lse_off = round_up64(w.ticket_bytes, 256);
   w.o_off = w.lse_off + round_up64((uint64_t)w.slots * s.hb * group * 4, 256);
   w.total = w.o_off + round_up64((uint64_t)w.slots * s.hb * group * a->head_dim * 4, 256);

@@ -181,6 +181,23 @@ def test_wide_groups(hq, hkv, d, kv_dtype, kernel):
         helpers.assert_close(_run(case, kernel, splits), ref, what=f"group {hq // hkv} {kv_dtype}")
 
 
+@pytest.mark.parametrize("kv_dtype,lens", [("fp16", (40000,)), ("int8", (30000, 700)), ("fp16", (9000, 9000, 20))])
+def test_deep_merges_of_long_requests(kv_dtype, lens):
+    """One request cut over (nearly) every worker: its partials are merged in two levels."""
+    case = cases.Case("deep", 32, 8, 128, 16, kv_dtype, lens, seed=41)
+    q_np, oc = cases.build(case)
+    ref, ref_lse = c_oracle.decode(q_np.astype(np.float32), oc, want_lse=True)
+    cache = helpers.to_device_cache(oc)
+    q = torch.from_numpy(q_np).cuda()
+    f32 = torch.empty(q.shape, dtype=torch.float32, device="cuda")
+    lse = torch.empty(q.shape[:2], dtype=torch.float32, device="cuda")
+    for _ in range(2):  # twice: the counters must be left clean
+        out = pda.paged_decode(q, cache, kernel="stream", result_f32=f32, result_lse=lse)
+        helpers.assert_close(out, ref, what=f"deep {kv_dtype} {lens}")
+        helpers.assert_close(f32, ref, what="deep fp32")
+        assert np.abs(lse.cpu().numpy() - ref_lse).max() < 5e-3
+
+
 def test_merge_partials_matches_oracle():
     rng = np.random.Generator(np.random.PCG64(77))
     po_ = rng.standard_normal((5, 3, 14, 64), dtype=np.float32)
