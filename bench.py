@@ -38,7 +38,7 @@ METRIC = "decode_attn_hbm_gbs"
 # workload shape (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic KV bytes of
 # the captured case; see profiles/).  Traffic grows in proportion to the tokens processed, so
 # the ratio scales a full launch.
-NCU_TRAFFIC_RATIO = {"c2": 1.013, "c3": 1.020}
+NCU_TRAFFIC_RATIO = {"c2": 1.0136, "c3": 1.024, "c4": 1.015, "c5": 1.025}
 L2_BYTES = 126 << 20
 FALLBACK_HBM_GBS = 6650.0
 
