@@ -214,6 +214,12 @@ PD_API int pd_merge(const PdMergeArgs* args);
 /* Dense dequantised fp16 gather (see PdGatherArgs). */
 PD_API int pd_gather(const PdGatherArgs* args);
 
+/* Failure-path self-test with no counterpart in the reference: runs the kernels' bounded
+ * mbarrier wait on a barrier nothing ever completes.  After `limit_ns` (at most one second) the
+ * wait gives up, ORs PD_DEV_TIMEOUT into *status (a device word) and the kernel returns
+ * normally: the context stays usable.  Lets a host check the give-up path without a fault. */
+PD_API int pd_selftest_bounded_wait(uint32_t* status, uint64_t limit_ns, void* stream);
+
 /* Stores this step's keys and values into their cache slots, quantising to the cache's
  * element type with the reference's rules, bit for bit (see PdCacheWriteArgs). */
 PD_API int pd_cache_write(const PdCacheWriteArgs* args);

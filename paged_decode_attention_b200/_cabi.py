@@ -87,7 +87,7 @@ class PdGatherArgs(ctypes.Structure):
 
 EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
            "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather",
-           "pd_decode_static", "pd_cache_write")
+           "pd_decode_static", "pd_cache_write", "pd_selftest_bounded_wait")
 
 STATIC_SCRATCH_BYTES = 8 << 20
 ERR_TOO_LARGE = -5
@@ -130,6 +130,8 @@ def load() -> ctypes.CDLL:
     lib.pd_merge.argtypes = [ctypes.POINTER(PdMergeArgs)]
     lib.pd_gather.restype = ctypes.c_int
     lib.pd_gather.argtypes = [ctypes.POINTER(PdGatherArgs)]
+    lib.pd_selftest_bounded_wait.restype = ctypes.c_int
+    lib.pd_selftest_bounded_wait.argtypes = [_c_vp, _c_u64, _c_vp]
     lib.pd_cache_write.restype = ctypes.c_int
     lib.pd_cache_write.argtypes = [ctypes.POINTER(PdCacheWriteArgs)]
     _lib = lib

@@ -66,7 +66,7 @@ template <int KV, int D, int HB, bool SCALED>
 struct StreamCfg {
   static constexpr int EB = is_16bit(KV) ? 2 : 1;
   static constexpr int ROWB = D * EB;
-  static_assert(ROWB == 128 || ROWB == 256, "row must be one or two 128-byte chunks");
+  static_assert(ROWB == 128 || ROWB == 256 || ROWB == 512, "row must be 1, 2 or 4 128-byte chunks");
   static constexpr int NC = ROWB / 128;                     // 128-byte chunks per row
   static constexpr int BOX_ELEMS = 128 / EB;                // elements of one chunk
   static constexpr int WARPS_PER_WORKER = HB + 1;
@@ -128,14 +128,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Waits for a barrier phase for at most kWaitLimitNs.  Returns false (after raising the CTA's
 // abort flag and PD_DEV_TIMEOUT) when it gives up or when another warp already aborted.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t* status,
-                                            volatile int* abort_flag, bool heed_abort) {
+                                            volatile int* abort_flag, bool heed_abort,
+                                            unsigned long long limit_ns = kWaitLimitNs) {
   const unsigned long long t0 = global_timer_ns();
   unsigned spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (heed_abort && *abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicOr(status, PD_DEV_TIMEOUT);
         return false;
@@ -581,7 +582,7 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
       for_ranges([&](int slot0, int n, int stride) {
         const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
         const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
-#pragma unroll 2
+#pragma unroll(J > 8 ? 1 : 2)
         for (int i = phase; i < n; i += sp_n) {
           const float lse = __ldcg(lp + (int64_t)i * stride * hg);
           float4 x[J];
@@ -1040,8 +1041,12 @@ struct Shape {
 static Shape derive(const PdDecodeArgs* a) {
   Shape s;
   s.hb = head_block(a->num_kv_heads);
+  // head_dim 256 at 16 bits: a stage of 8 consumer warps' worth would be 128 KB, so at most
+  // four heads per block and four consumer warps per CTA (three 64 KB stages)
+  const bool wide = a->head_dim * (is_16bit(a->kv_dtype) ? 2 : 1) == 512;
+  if (wide && s.hb > 4) s.hb = 4;
   s.nhb = a->num_kv_heads / s.hb;
-  s.wpc = base_workers_per_cta(s.hb);
+  s.wpc = wide ? 4 / s.hb : base_workers_per_cta(s.hb);
   s.splits = a->num_splits > 0 ? a->num_splits : 1;
   const long long nv = (long long)s.nhb * a->batch * s.splits;
   s.nvseq = nv > INT32_MAX ? INT32_MAX : (int)nv;
@@ -1082,7 +1087,7 @@ int stream_supports(const PdDecodeArgs* a) {
   if ((a->kv_dtype == PD_KV_BF16) != (a->io_dtype == PD_IO_BF16)) return PD_ERR_UNSUPPORTED;
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   const int rowb = a->head_dim * eb;
-  if (rowb != 128 && rowb != 256) return PD_ERR_UNSUPPORTED;
+  if (rowb != 128 && rowb != 256 && !(rowb == 512 && eb == 2)) return PD_ERR_UNSUPPORTED;
   if (a->batch <= 0) return PD_ERR_UNSUPPORTED;
   const int group = a->num_q_heads / a->num_kv_heads;
   if (group > 16) return PD_ERR_UNSUPPORTED;
@@ -1217,10 +1222,15 @@ static cudaError_t launch_wpc(const StreamParams& sp, const CUtensorMap& mk, con
 template <int KV, int D, int HB, bool SCALED, int NG>
 static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
                              int grid, uint32_t smem, cudaStream_t st) {
-  if constexpr (HB == 8 && !is_16bit(KV)) {
-    if (sp.wpc == 2) return launch_wpc<KV, D, HB, SCALED, NG, 2>(sp, mk, mv, grid, smem, st);
+  if constexpr (D == 256) {
+    static_assert(HB <= 4, "head_dim 256 runs at most four heads per block");
+    return launch_wpc<KV, D, HB, SCALED, NG, 4 / HB>(sp, mk, mv, grid, smem, st);
+  } else {
+    if constexpr (HB == 8 && !is_16bit(KV)) {
+      if (sp.wpc == 2) return launch_wpc<KV, D, HB, SCALED, NG, 2>(sp, mk, mv, grid, smem, st);
+    }
+    return launch_wpc<KV, D, HB, SCALED, NG, base_workers_per_cta(HB)>(sp, mk, mv, grid, smem, st);
   }
-  return launch_wpc<KV, D, HB, SCALED, NG, base_workers_per_cta(HB)>(sp, mk, mv, grid, smem, st);
 }
 
 // groups of up to 8 query heads fit one 8-wide n-tile, up to 16 need two
@@ -1235,7 +1245,9 @@ template <int KV, int D, bool SCALED>
 static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
                              int grid, uint32_t smem, cudaStream_t st) {
   switch (hb) {
-    case 8: return launch_one<KV, D, 8, SCALED>(sp, mk, mv, grid, smem, st);
+    case 8:
+      if constexpr (D != 256) return launch_one<KV, D, 8, SCALED>(sp, mk, mv, grid, smem, st);
+      else return cudaErrorInvalidValue;
     case 4: return launch_one<KV, D, 4, SCALED>(sp, mk, mv, grid, smem, st);
     case 2: return launch_one<KV, D, 2, SCALED>(sp, mk, mv, grid, smem, st);
     default: return launch_one<KV, D, 1, SCALED>(sp, mk, mv, grid, smem, st);
@@ -1279,9 +1291,11 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   cudaError_t e;
   if (a->kv_dtype == PD_KV_F16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+        : a->head_dim == 256 ? launch_hb<PD_KV_F16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_BF16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+        : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
     e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
@@ -1376,9 +1390,11 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   cudaError_t e;
   if (a->kv_dtype == PD_KV_F16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+        : a->head_dim == 256 ? launch_hb<PD_KV_F16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_BF16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+        : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
     e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
@@ -1389,7 +1405,30 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
+
+// A wait nobody ends, on purpose: one warp initialises an mbarrier that no thread and no copy
+// ever arrives on and waits for it with the kernel's own bounded wait.  The wait must give up
+// after `limit_ns`, raise PD_DEV_TIMEOUT in the status word and return normally.
+__global__ void bounded_wait_selftest_kernel(uint32_t* status, unsigned long long limit_ns) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(addr, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  mbar_wait_slow(addr, 0, status, &abort_flag, true, limit_ns);
+}
+
 }  // namespace pd
+
+extern "C" PD_API int pd_selftest_bounded_wait(uint32_t* status, uint64_t limit_ns, void* stream) {
+  if (!status || limit_ns == 0 || limit_ns > 1000000000ull) return PD_ERR_INVALID_ARG;
+  pd::bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
 
 // Decode step for callers that cannot hand over scratch memory: see include/paged_decode.h.
 // The first call on a device looks up the scratch array's device address (one

@@ -198,6 +198,16 @@ def test_deep_merges_of_long_requests(kv_dtype, lens):
         assert np.abs(lse.cpu().numpy() - ref_lse).max() < 5e-3
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("hq,hkv,io", [(16, 4, "fp16"), (8, 1, "fp16"), (16, 2, "bf16"), (32, 8, "fp16")])
+def test_head_dim_256(hq, hkv, io, kernel):
+    case = cases.Case("d256", hq, hkv, 256, 16, io, (700, 33, 2100), seed=53, io_dtype=io)
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    for splits in (None, 2):
+        helpers.assert_close(_run(case, kernel, splits), ref, bf16=io == "bf16", what=f"D256 {hq}/{hkv} {io}")
+
+
 def test_merge_partials_matches_oracle():
     rng = np.random.Generator(np.random.PCG64(77))
     po_ = rng.standard_normal((5, 3, 14, 64), dtype=np.float32)
@@ -300,3 +310,23 @@ def test_cache_write_flags_slots_outside_the_pool():
     torch.cuda.synchronize()
     assert int(status.item()) & _cabi.DEV_BAD_BLOCK
     assert float(cache.k_cache[0, 5].min()) == 1.0 and float(cache.k_cache.sum()) == 2 * 64
+
+
+def test_bounded_wait_gives_up_and_leaves_the_context_usable():
+    """Failure detection without a fault: a wait nothing ends runs out after its limit, reports
+    PD_DEV_TIMEOUT through the status word, and the next decode on the same context is correct."""
+    import time
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.perf_counter()
+    rc = _cabi.load().pd_selftest_bounded_wait(status.data_ptr(), 50_000_000,
+                                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert int(status.item()) & _cabi.DEV_TIMEOUT
+    assert 0.04 <= took < 1.0, took
+    case = cases.BY_NAME["llama8b_b2_s65"]
+    q_np, oc = cases.build(case)
+    out = pda.paged_decode(torch.from_numpy(q_np).cuda(), helpers.to_device_cache(oc))
+    helpers.assert_close(out, c_oracle.decode(q_np.astype(np.float32), oc), what="after timeout")
