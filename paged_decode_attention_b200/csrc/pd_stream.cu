@@ -1,1026 +1,15 @@
-// Streaming decode kernel for sm_100a: a persistent grid of one CTA per SM.
-//
-// Work decomposition.  Every request's KV range (or every explicit split of it) for one block
-// of HB kv heads is a "virtual sequence" of 16-token tiles.  All virtual sequences are laid end
-// to end and the tile sequence is cut into equal contiguous shares, one per worker.  A worker
-// is HB consumer warps (one per kv head of the block) plus one producer warp; a CTA hosts
-// 8/HB workers (at most 4).  Shares are balanced to one tile whatever the length distribution,
-// and they are derived on the device from seq_lens, so the host never synchronises.
-//
-// Data movement.  The producer warp resolves each tile's page through the block table (32
-// tiles' entries are fetched with one coalesced load ahead of use) and issues tiled TMA loads
-// (cp.async.bulk.tensor) of the K and V boxes [HB heads][16 tokens][128 B] with the 128-byte
-// swizzle into a ring of shared-memory stages; completion is tracked by mbarriers
-// (full/empty per stage).  Per-(token, head) scales ride along as untiled bulk copies.  The
-// ring runs across request boundaries, so HBM requests never drain between requests.
-//
-// Math.  Each consumer warp keeps the (padded to 16) query rows of its group as mma A
-// fragments in registers, computes S = Q K^T with mma.sync m16n8k16 (K rows via ldmatrix, or
-// 16-byte shared loads plus in-register int8 / e5m2 -> f16 conversion), applies a base-2
-// online softmax with warp shuffles (the reference's recurrence,
-// pagedattn/triton_decode.py:159-166), and accumulates O += P V in fp32.  Scales factor out of
-// both contractions: S is multiplied by the K scale per token, P by the V scale per token, so
-// 8-bit pages are only ever converted, never multiplied element-wise.
-//
-// Results.  A (worker, virtual sequence) segment that covers a whole unsplit request writes
-// its output row directly; any other segment writes a normalised fp32 partial plus its base-2
-// log-sum-exp into slot (worker + virtual sequence) of the scratch and takes a ticket on the
-// (request, kv head) counter; the warp whose ticket completes the count merges the request's
-// slots in place (pagedattn/triton_decode.py:221-240).  No second kernel, and no warp ever
-// waits for another.
-//
-// Every wait is bounded: a wait that exceeds its limit sets PD_DEV_TIMEOUT in the status word,
-// raises the CTA's abort flag, and all warps leave their loops; the producer then waits (again
-// bounded) for the copies it still has in flight before the CTA exits.
+// Host side of the streaming decode kernel (pd_stream_kernel.cuh): which requests it serves, its
+// shared-memory and scratch plans, TMA tensor maps, kernel dispatch, the allocation-free entry
+// point pd_decode_static and the bounded-wait self-test.
 #include <cuda.h>
 
 #include <mutex>
 #include <vector>
 
 #include "pd_stream.h"
+#include "pd_stream_kernel.cuh"
 
 namespace pd {
-
-// ---------------------------------------------------------------------------------------------
-// configuration
-// ---------------------------------------------------------------------------------------------
-constexpr int kTileTokens = 16;
-
-// 16-bit page element types: both are moved and multiplied as they are
-__host__ __device__ constexpr bool is_16bit(int kv) { return kv == PD_KV_F16 || kv == PD_KV_BF16; }
-constexpr int kMaxVseq = 4096;
-constexpr int kMinTilesPerWorker = 4;
-constexpr int kMergeRadix = 8;
-constexpr int kSmemLimit = 227 * 1024;
-constexpr int kMaxStages = 12;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-
-// Workers per CTA: eight consumer warps' worth (at most four workers).  Kernels for 8-bit pages
-// with eight heads per block also exist with two workers (sixteen consumer warps): an 8-bit tile
-// carries half the bytes for the same instruction count, and the extra warps hide the
-// conversion latency.  Every worker adds a segment to each request it touches, so the host
-// picks two only for batches with many requests (see derive()).
-__host__ __device__ constexpr int base_workers_per_cta(int hb) { return 8 / hb < 4 ? 8 / hb : 4; }
-
-template <int KV, int D, int HB, bool SCALED>
-struct StreamCfg {
-  static constexpr int EB = is_16bit(KV) ? 2 : 1;
-  static constexpr int ROWB = D * EB;
-  static_assert(ROWB == 128 || ROWB == 256 || ROWB == 512, "row must be 1, 2 or 4 128-byte chunks");
-  static constexpr int NC = ROWB / 128;                     // 128-byte chunks per row
-  static constexpr int BOX_ELEMS = 128 / EB;                // elements of one chunk
-  static constexpr int WARPS_PER_WORKER = HB + 1;
-  static constexpr int CHUNK_BYTES = HB * kTileTokens * 128; // one TMA box
-  static constexpr int TILE_BYTES = NC * CHUNK_BYTES;        // K (or V) of one tile
-  static constexpr int SCALE_BYTES = SCALED ? 2048 : 0;      // K scales at +0, V scales at +1024
-  static constexpr int STAGE_BYTES = 2 * TILE_BYTES + SCALE_BYTES;
-  static constexpr int KSTEPS = D / 16;
-  static constexpr int MT = D / 16;                          // 16-row tiles of head_dim in O^T
-};
-
-struct StreamParams {
-  Params p;
-  int32_t nvseq, nhb, splits, nstage, wpc;
-  uint32_t bar_off, meta_off, misc_off, prefix_off;
-  int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
-  uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
-};
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void fence_barrier_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Waits for a barrier phase for at most kWaitLimitNs.  Returns false (after raising the CTA's
-// abort flag and PD_DEV_TIMEOUT) when it gives up or when another warp already aborted.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t* status,
-                                            volatile int* abort_flag, bool heed_abort,
-                                            unsigned long long limit_ns = kWaitLimitNs) {
-  const unsigned long long t0 = global_timer_ns();
-  unsigned spins = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (heed_abort && *abort_flag) return false;
-      if (global_timer_ns() - t0 > limit_ns) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, PD_DEV_TIMEOUT);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status,
-                                          volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, status, abort_flag, true);
-}
-
-// Tiled TMA load of one 4-D box into shared memory; completion is counted on `bar`.
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
-                                          uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"((unsigned long long)src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t r;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
-  return r;
-}
-__device__ __forceinline__ float lds_half(uint32_t addr) {
-  unsigned short h;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
-  return __half2float(__ushort_as_half(h));
-}
-// D(16x8, f32) += A(16x16, f16) * B(16x8, f16)
-__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                        uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// the same with bf16 inputs
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
-      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// bf16 pages are multiplied as bf16 (q, P and the output are bf16 too); every other page type
-// reaches the tensor core as f16
-template <int KV>
-__device__ __forceinline__ void mma_kv(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if constexpr (KV == PD_KV_BF16) mma_bf16(c, a, b0, b1);
-  else mma_f16(c, a, b0, b1);
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-  const __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// Two floats -> packed 16-bit pair in the type q and out use (bf16 with bf16 pages, else f16).
-template <int KV>
-__device__ __forceinline__ uint32_t pack_io2(float lo, float hi) {
-  if constexpr (KV == PD_KV_BF16) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-  } else {
-    return pack_half2(lo, hi);
-  }
-}
-template <int KV>
-__device__ __forceinline__ void store_io(void* row, int col, float x) {
-  if constexpr (KV == PD_KV_BF16) ((__nv_bfloat16*)row)[col] = __float2bfloat16_rn(x);
-  else ((__half*)row)[col] = __float2half_rn(x);
-}
-
-// Two stored 8-bit elements (bytes `lo_sel`, `lo_sel + 1` of w) -> packed f16x2, exactly.
-template <int KV>
-__device__ __forceinline__ uint32_t cvt_pair(uint32_t w, bool upper) {
-  if constexpr (KV == PD_KV_E5M2) {
-    // e5m2 is the high byte of an f16: place each byte above a zero byte
-    return __byte_perm(w, 0u, upper ? 0x3424u : 0x1404u);
-  } else {
-    // int8: w already holds x ^ 0x80 (= x + 128 as unsigned); 0x6400 | u is the f16 1024 + u,
-    // so subtracting 1152 leaves x
-    const uint32_t h = __byte_perm(w, 0x64646464u, upper ? 0x4342u : 0x4140u);
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h),
-                              __half2half2(__ushort_as_half((unsigned short)0x6480)));
-    return *reinterpret_cast<const uint32_t*>(&r);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// schedule helpers (shared by producer, consumers and the merge kernel)
-// ---------------------------------------------------------------------------------------------
-struct VseqInfo {
-  int hb, b, split, lo, hi;
-};
-
-__device__ __forceinline__ int clamp_len(const Params& p, int b) {
-  int len = __ldg(p.seq_lens + b);
-  const long long cap = (long long)p.max_blocks * p.page;
-  if (len < 0) len = 0;
-  if (len > cap) {
-    if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
-    len = (int)cap;
-  }
-  return len;
-}
-
-__device__ __forceinline__ VseqInfo vseq_info(const StreamParams& sp, int v) {
-  VseqInfo i;
-  i.split = v % sp.splits;
-  const int t = v / sp.splits;
-  i.b = t % sp.p.batch;
-  i.hb = t / sp.p.batch;
-  split_range(clamp_len(sp.p, i.b), i.split, sp.splits, sp.p.block_n, i.lo, i.hi);
-  return i;
-}
-
-// Largest v in [0, n) with prefix[v] <= g (prefix is non-decreasing, prefix[0] = 0, g < prefix[n]).
-__device__ __forceinline__ int find_vseq(const int* prefix, int n, int g) {
-  int lo = 0, hi = n;  // invariant: prefix[lo] <= g < prefix[hi]
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (prefix[mid] <= g) lo = mid;
-    else hi = mid;
-  }
-  return lo;
-}
-
-// int8 pair -> f16x2 holding 1152 + x (w is x ^ 0x80 per byte): one prmt, no subtraction.
-__device__ __forceinline__ uint32_t cvt_pair_biased(uint32_t w, bool upper) {
-  return __byte_perm(w, 0x64646464u, upper ? 0x4342u : 0x4140u);
-}
-// Transposes an 8x8 matrix of 16-bit elements held one row-pair per thread (ldmatrix layout).
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
-  uint32_t y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-
-// One 16-token tile of one kv head for one consumer warp.  The products are taken with the
-// tokens on the M axis of the mma and the query heads of the group on its N axis ("swapped"):
-//   S^T[16 tokens x 8 heads] = K[16 x D] * Q^T,   O^T[D x 8 heads] += V^T[D x 16] * P^T
-// so a group of up to 8 heads fills the 8-wide N dimension instead of padding a 16-row M
-// (NG = 2 covers groups of 9..16).  Thread (g = lane / 4, t = lane % 4) owns tokens g and g + 8
-// of S^T and heads 2t, 2t + 1 (+ 8 per n-tile), the same heads it owns in O^T, so the softmax
-// state (m, l) stays in the thread; P^T reaches the B-operand layout with two movmatrix.
-// `kbase` is the warp's K rows in the stage (V follows at TILE_BYTES), `scales` the address of
-// this head's K scale of token 0 (V scales 1024 bytes further, token pitch hkv * 2).
-// MASKED tiles hold fewer than 16 live tokens (`valid`); full tiles skip every mask.
-template <int KV, int D, int HB, bool SCALED, int NG, bool MASKED>
-__device__ __forceinline__ void consume_tile(
-    const uint32_t kbase, const uint32_t scales, const int hkv, const int valid,
-    const float scale_log2, const int lane,
-    const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qbias)[NG][2],
-    float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4]) {
-  using C = StreamCfg<KV, D, HB, SCALED>;
-  constexpr unsigned kFull = 0xffffffffu;
-  const int gq = lane >> 2, tq = lane & 3;
-  const uint32_t vbase = kbase + C::TILE_BYTES;
-
-  // ---- S^T = K Q^T ------------------------------------------------------------------------------
-  float s[NG][4];
-#pragma unroll
-  for (int ng = 0; ng < NG; ++ng) s[ng][0] = s[ng][1] = s[ng][2] = s[ng][3] = 0.f;
-  if constexpr (is_16bit(KV)) {
-    // A fragments by ldmatrix: matrices (tokens 0-7, lo), (8-15, lo), (0-7, hi), (8-15, hi) where
-    // lo/hi are the two 16-byte chunks of the k-step
-    const int mi = lane >> 3;
-    const int token = 8 * (mi & 1) + (lane & 7);
-    const uint32_t row = kbase + token * 128;
-#pragma unroll
-    for (int ks = 0; ks < C::KSTEPS; ++ks) {
-      const int chunk = ((2 * ks) & 7) + (mi >> 1);
-      uint32_t a[4];
-      ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
-#pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
-    }
-  } else {
-    // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each row give
-    // eight words, word i of chunk jh feeding k-step 4*jh + i
-    const uint32_t row0 = kbase + gq * 128, row1 = row0 + 8 * 128;
-#pragma unroll
-    for (int jh = 0; jh < 2; ++jh) {
-      const uint32_t ch = (uint32_t)((2 * tq + jh) ^ (gq & 7)) << 4;
-      uint32_t w0[4], w1[4];
-      lds128(row0 + ch, w0);
-      lds128(row1 + ch, w1);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t a[4];
-        if constexpr (KV == PD_KV_I8) {
-          const uint32_t x0 = w0[i] ^ 0x80808080u, x1 = w1[i] ^ 0x80808080u;
-          a[0] = cvt_pair_biased(x0, false);
-          a[1] = cvt_pair_biased(x1, false);
-          a[2] = cvt_pair_biased(x0, true);
-          a[3] = cvt_pair_biased(x1, true);
-        } else {
-          a[0] = cvt_pair<KV>(w0[i], false);
-          a[1] = cvt_pair<KV>(w1[i], false);
-          a[2] = cvt_pair<KV>(w0[i], true);
-          a[3] = cvt_pair<KV>(w1[i], true);
-        }
-#pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * jh + i][ng][0], qb[4 * jh + i][ng][1]);
-      }
-    }
-  }
-
-  // ---- scale, mask, online softmax; P^T into B-operand layout ---------------------------------
-  float f0 = scale_log2, f1 = scale_log2;  // tokens g and g + 8
-  float vs0 = 1.f, vs1 = 1.f;              // their V scales (times 256)
-  if constexpr (SCALED) {
-    const uint32_t sa = scales + gq * hkv * 2;
-    f0 *= lds_half(sa);
-    f1 *= lds_half(sa + 8 * hkv * 2);
-    vs0 = lds_half(sa + 1024) * 256.f;
-    vs1 = lds_half(sa + 1024 + 8 * hkv * 2) * 256.f;
-  }
-  uint32_t pb[NG][2];
-  float alpha[NG][2];
-  bool moved = false;
-#pragma unroll
-  for (int ng = 0; ng < NG; ++ng) {
-    float x0 = s[ng][0], x1 = s[ng][1], x2 = s[ng][2], x3 = s[ng][3];
-    if constexpr (KV == PD_KV_I8) {
-      x0 -= qbias[ng][0];
-      x1 -= qbias[ng][1];
-      x2 -= qbias[ng][0];
-      x3 -= qbias[ng][1];
-    }
-    x0 *= f0;
-    x1 *= f0;
-    x2 *= f1;
-    x3 *= f1;
-    if constexpr (MASKED) {
-      if (gq >= valid) x0 = x1 = -INFINITY;
-      if (gq + 8 >= valid) x2 = x3 = -INFINITY;
-    }
-    float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);  // heads 2t, 2t+1 over the thread's tokens
-#pragma unroll
-    for (int sh = 4; sh < 32; sh <<= 1) {
-      mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, sh));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, sh));
-    }
-    const float mn0 = fmaxf(m[ng][0], mx0), mn1 = fmaxf(m[ng][1], mx1);  // finite: token 0 is live
-    alpha[ng][0] = fast_exp2(m[ng][0] - mn0);
-    alpha[ng][1] = fast_exp2(m[ng][1] - mn1);
-    moved = moved || alpha[ng][0] != 1.f || alpha[ng][1] != 1.f;
-    m[ng][0] = mn0;
-    m[ng][1] = mn1;
-    const float p0 = fast_exp2(x0 - mn0), p1 = fast_exp2(x1 - mn1);
-    const float p2 = fast_exp2(x2 - mn0), p3 = fast_exp2(x3 - mn1);
-    l[ng][0] = l[ng][0] * alpha[ng][0] + (p0 + p2);
-    l[ng][1] = l[ng][1] * alpha[ng][1] + (p1 + p3);
-    // (token g | g+8, heads 2t, 2t+1) -> (tokens 2t, 2t+1 | 2t+8, 2t+9, head g)
-    pb[ng][0] = movmatrix_trans(SCALED ? pack_io2<KV>(p0 * vs0, p1 * vs0) : pack_io2<KV>(p0, p1));
-    pb[ng][1] = movmatrix_trans(SCALED ? pack_io2<KV>(p2 * vs1, p3 * vs1) : pack_io2<KV>(p2, p3));
-  }
-  // the running maxima settle after the first tiles; skip the rescale when nobody's moved
-  if (__any_sync(kFull, moved)) {
-#pragma unroll
-    for (int mt = 0; mt < C::MT; ++mt) {
-#pragma unroll
-      for (int ng = 0; ng < NG; ++ng) {
-        o[mt][ng][0] *= alpha[ng][0];
-        o[mt][ng][1] *= alpha[ng][1];
-        o[mt][ng][2] *= alpha[ng][0];
-        o[mt][ng][3] *= alpha[ng][1];
-      }
-    }
-  }
-
-  // ---- O^T += V^T P^T ---------------------------------------------------------------------------
-  // Rows of V past `valid` hold whatever the page holds.  Every int8 byte is a finite number,
-  // so P = 0 already removes it; f16 / e5m2 garbage may be NaN and is zeroed in masked tiles.
-  constexpr bool kMaskV = MASKED && KV != PD_KV_I8;
-  uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // tokens (2t, 2t+1), (2t+8, 2t+9)
-  if constexpr (kMaskV) {
-    keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
-    keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
-  }
-  if constexpr (is_16bit(KV)) {
-    // transposed 8x8 matrices (tokens 0-7, lo), (0-7, hi), (8-15, lo), (8-15, hi) of the 16
-    // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
-    const int mi = lane >> 3;
-    const int token = 8 * (mi >> 1) + (lane & 7);
-    const uint32_t row = vbase + token * 128;
-#pragma unroll
-    for (int mt = 0; mt < C::MT; ++mt) {
-      const int chunk = ((2 * mt) & 7) + (mi & 1);
-      uint32_t a[4];
-      ldmatrix_x4_trans(row + (mt >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
-      if constexpr (kMaskV) {
-        a[0] &= keep_lo;
-        a[1] &= keep_lo;
-        a[2] &= keep_hi;
-        a[3] &= keep_hi;
-      }
-#pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
-    }
-  } else {
-    // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of head_dim
-    // columns 32*jj + 4*g .. +3 and transposes bytes in registers.  m-tile 2*jj + h then holds
-    // column 32*jj + 4*g + 2*h in its row g and column + 1 in its row g + 8; the epilogue
-    // writes them back in order.
-    const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
-#pragma unroll
-    for (int jj = 0; jj < D / 32; ++jj) {
-      uint32_t r[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int chunk = 2 * jj + (gq >> 2);
-        r[k] = lds32(vbase + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) + ((gq & 3) << 2));
-        if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
-      }
-      // bytes (c0, c2) and (c1, c3) of the token pairs side by side
-      const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
-      const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t a[4];
-        if constexpr (KV == PD_KV_I8) {
-          // int8 values enter as 1152 + x (one prmt each); a second mma with the constant
-          // -1152 on the same P^T takes the surplus out again inside the accumulator, tile by
-          // tile, so the sum never carries the bias
-          a[0] = cvt_pair_biased(e01, h != 0);
-          a[1] = cvt_pair_biased(o01, h != 0);
-          a[2] = cvt_pair_biased(e23, h != 0);
-          a[3] = cvt_pair_biased(o23, h != 0);
-          const uint32_t neg[4] = {0xE480E480u, 0xE480E480u, 0xE480E480u, 0xE480E480u};
-#pragma unroll
-          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], neg, pb[ng][0], pb[ng][1]);
-        } else {
-          a[0] = cvt_pair<KV>(e01, h != 0);
-          a[1] = cvt_pair<KV>(o01, h != 0);
-          a[2] = cvt_pair<KV>(e23, h != 0);
-          a[3] = cvt_pair<KV>(o23, h != 0);
-        }
-        if constexpr (kMaskV) {
-          a[0] &= keep_lo;
-          a[1] &= keep_lo;
-          a[2] &= keep_hi;
-          a[3] &= keep_hi;
-        }
-#pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], a, pb[ng][0], pb[ng][1]);
-      }
-    }
-  }
-}
-
-// Segments (worker, virtual sequence) that cover request b / head block hb, in the order the
-// merge visits them: for every split with tiles, the workers first .. last of its tile range.
-template <typename F>
-__device__ __forceinline__ void for_each_segment(const int* prefix, int per, int v0, int splits, F&& f) {
-  for (int s = 0; s < splits; ++s) {
-    const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
-    if (last <= first) continue;
-    for (int wk = first / per; wk <= (last - 1) / per; ++wk) f(wk + v0 + s);
-  }
-}
-
-// Log-sum-exp merge of every partial of one (request, kv head), run by the consumer warp whose
-// partial arrived last (pagedattn/triton_decode.py:221-240 for the arithmetic).  The eight
-// 4-lane groups of the warp are split between rows and segments: with RP = the group size
-// rounded up to a power of two (at most 8), lane group q handles row q % RP and the segments
-// i with i % (8 / RP) == q / RP; a lane owns the head_dim floats 16*j + 4*c .. +3 of its row.
-// Small groups thus spread a long segment list (dozens for one long-context request) over more
-// lanes.  The per-phase sums are combined with shuffles.  Partials were written by other SMs:
-// they are read with ld.global.cg after the ticket's fence.
-template <int KV, int D>
-__device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, int per, int v0,
-                                           int splits, int hg, int head_in_block, int b, int kvh,
-                                           int lane, int rslot0 = 0, int rn = 0, int rstride = 1,
-                                           int dst_slot = -1) {
-  // Default: merge every segment the schedule gives the unit and write the final rows.  With
-  // rn > 0 the inputs are instead the rn slots rslot0, rslot0 + rstride, ...; with dst_slot >= 0
-  // the result goes back into that slot as a normalised partial (first level of a deep merge).
-  auto for_ranges = [&](auto&& f) {
-    if (rn > 0) {
-      f(rslot0, rn, rstride);
-      return;
-    }
-    for (int s = 0; s < splits; ++s) {
-      const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
-      if (last <= first) continue;
-      f(first / per + v0 + s, (last - 1) / per - first / per + 1, 1);
-    }
-  };
-  constexpr int J = D / 16;
-  constexpr unsigned kFull = 0xffffffffu;
-  const int q = lane >> 2, c = lane & 3;
-  int rp = 1;
-  while (rp < p.group && rp < 8) rp <<= 1;
-  const int sp_n = 8 / rp;        // segment phases
-  const int phase = q / rp;
-  for (int r0 = 0; r0 < p.group; r0 += 8) {
-    const int row = r0 + q % rp;
-    const bool live = row < p.group;
-    const int64_t local = (int64_t)head_in_block * p.group + (live ? row : 0);
-    float m = -INFINITY;
-    for_ranges([&](int slot0, int n, int stride) {
-      const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
-#pragma unroll 4
-      for (int i = phase; i < n; i += sp_n) m = fmaxf(m, __ldcg(lp + (int64_t)i * stride * hg));
-    });
-    for (int sh = 4 * rp; sh < 32; sh <<= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, sh));
-    float denom = 0.f;
-    float acc[J][4];
-#pragma unroll
-    for (int j = 0; j < J; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    if (m > -INFINITY) {
-      for_ranges([&](int slot0, int n, int stride) {
-        const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
-        const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
-#pragma unroll(J > 8 ? 1 : 2)
-        for (int i = phase; i < n; i += sp_n) {
-          const float lse = __ldcg(lp + (int64_t)i * stride * hg);
-          float4 x[J];
-#pragma unroll
-          for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * stride * hg * (D / 4) + 4 * j);
-          const float wgt = lse > -INFINITY ? exp2f(lse - m) : 0.f;
-          denom += wgt;
-#pragma unroll
-          for (int j = 0; j < J; ++j) {
-            acc[j][0] = fmaf(wgt, x[j].x, acc[j][0]);
-            acc[j][1] = fmaf(wgt, x[j].y, acc[j][1]);
-            acc[j][2] = fmaf(wgt, x[j].z, acc[j][2]);
-            acc[j][3] = fmaf(wgt, x[j].w, acc[j][3]);
-          }
-        }
-      });
-    }
-    for (int sh = 4 * rp; sh < 32; sh <<= 1) {
-      denom += __shfl_xor_sync(kFull, denom, sh);
-#pragma unroll
-      for (int j = 0; j < J; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[j][e] += __shfl_xor_sync(kFull, acc[j][e], sh);
-      }
-    }
-    if (!live || phase != 0) continue;
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    if (dst_slot >= 0) {
-      // first level of a deep merge: the chunk's result replaces the partial in its first slot
-      const int64_t sr = (int64_t)dst_slot * hg + local;
-#pragma unroll
-      for (int j = 0; j < J; ++j)
-        *reinterpret_cast<float4*>(p.part_o + sr * D + 16 * j + 4 * c) =
-            make_float4(acc[j][0] * inv, acc[j][1] * inv, acc[j][2] * inv, acc[j][3] * inv);
-      if (c == 0) p.part_lse[sr] = denom > 0.f ? m + log2f(denom) : -INFINITY;
-      continue;
-    }
-    const int hq = kvh * p.group + row;
-    __half* dst16 = p.out ? (__half*)p.out + (int64_t)b * p.o_sb + (int64_t)hq * p.o_sh : nullptr;
-    float* dst32 = p.res_o ? p.res_o + ((int64_t)b * p.hq + hq) * D : nullptr;
-#pragma unroll
-    for (int j = 0; j < J; ++j) {
-      const int col = 16 * j + 4 * c;
-      const float x0 = acc[j][0] * inv, x1 = acc[j][1] * inv, x2 = acc[j][2] * inv, x3 = acc[j][3] * inv;
-      if (dst16) {
-        uint2 pk;
-        pk.x = pack_io2<KV>(x0, x1);
-        pk.y = pack_io2<KV>(x2, x3);
-        *reinterpret_cast<uint2*>(dst16 + col) = pk;
-      }
-      if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
-    }
-    if (p.res_o && c == 0) p.res_lse[(int64_t)b * p.hq + hq] = denom > 0.f ? m + log2f(denom) : -INFINITY;
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// the kernel
-// ---------------------------------------------------------------------------------------------
-template <int KV, int D, int HB, bool SCALED, int NG, int WPC>
-__global__ void __launch_bounds__(WPC * (HB + 1) * 32, 1)
-stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v) {
-  using C = StreamCfg<KV, D, HB, SCALED>;
-  constexpr unsigned kFull = 0xffffffffu;
-  constexpr int kThreads = WPC * (HB + 1) * 32;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
-  uint8_t* smem = smem_raw + (base - raw_addr);
-  int* prefix = reinterpret_cast<int*>(smem + sp.prefix_off);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + sp.misc_off);
-
-  const Params& p = sp.p;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wl = warp / C::WARPS_PER_WORKER;    // worker within the CTA
-  const int role = warp % C::WARPS_PER_WORKER;  // < HB: consumer of that head; == HB: producer
-  const int nstage = sp.nstage;
-  const uint32_t stage0 = base + (uint32_t)wl * nstage * C::STAGE_BYTES;
-  const uint32_t full0 = base + sp.bar_off + (uint32_t)wl * nstage * 16;
-  const uint32_t empty0 = full0 + nstage * 8;
-  volatile int* meta = reinterpret_cast<volatile int*>(smem + sp.meta_off) + wl * nstage;
-
-  // ---- tiles per virtual sequence, then an inclusive scan: prefix[v] = first tile of v ------
-  const int nv = sp.nvseq;
-  for (int v = tid; v < nv; v += kThreads) {
-    const VseqInfo i = vseq_info(sp, v);
-    prefix[v + 1] = i.hi > i.lo ? (i.hi - i.lo + kTileTokens - 1) / kTileTokens : 0;
-  }
-  if (tid == 0) {
-    prefix[0] = 0;
-    *abort_flag = 0;
-  }
-  if (role == HB && lane == 0) {
-    for (int s = 0; s < nstage; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, HB);
-    }
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  __syncthreads();
-  if (warp == 0) {
-    int carry = 0;
-    for (int first = 1; first <= nv; first += 32) {
-      const int idx = first + lane;
-      int x = idx <= nv ? prefix[idx] : 0;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(kFull, x, o);
-        if (lane >= o) x += y;
-      }
-      if (idx <= nv) prefix[idx] = x + carry;
-      carry += __shfl_sync(kFull, x, 31);
-    }
-  }
-  __syncthreads();
-
-  const int total = prefix[nv];
-  const int workers = gridDim.x * WPC;
-  int per = (total + workers - 1) / workers;
-  if (per < kMinTilesPerWorker) per = kMinTilesPerWorker;
-  const int w = blockIdx.x * WPC + wl;  // global worker id
-  const long long g0l = (long long)w * per;
-  const int g0 = g0l < total ? (int)g0l : total;
-  const int g1 = g0 + per < total ? g0 + per : total;
-  if (blockIdx.x == 0) {
-    // requests without a single token are nobody's work: their rows are zero, their lse -inf
-    for (int u = tid; u < sp.nhb * p.batch; u += kThreads) {
-      if (prefix[(u + 1) * sp.splits] != prefix[u * sp.splits]) continue;
-      const int b = u % p.batch, hb = u / p.batch;
-      for (int h = hb * HB * p.group; h < (hb + 1) * HB * p.group; ++h) {
-        for (int d = 0; d < D; ++d) {
-          if (p.out) ((uint16_t*)p.out)[(int64_t)b * p.o_sb + (int64_t)h * p.o_sh + d] = 0;  // +0 in f16 and bf16
-          if (p.res_o) p.res_o[((int64_t)b * p.hq + h) * D + d] = 0.f;
-        }
-        if (p.res_o) p.res_lse[(int64_t)b * p.hq + h] = -INFINITY;
-      }
-    }
-  }
-  if (g0 >= g1) return;  // nothing for this worker (no barrier is used after this point)
-
-  // =============================== producer warp =============================================
-  if (role == HB) {
-    constexpr uint32_t kTileTx = 2u * C::TILE_BYTES;
-    int it = 0;
-    int vbase = find_vseq(prefix, nv, g0);
-    bool aborted = false;
-    for (int g = g0; g < g1 && !aborted; g += 32) {
-      const int myg = g + lane;
-      const bool act = myg < g1;
-      int mv = vbase;
-      if (act)
-        while (prefix[mv + 1] <= myg) ++mv;
-      vbase = __shfl_sync(kFull, mv, 0);
-      int phys = 0, tok = 0, hbi = 0, bad = 0;
-      if (act) {
-        const VseqInfo i = vseq_info(sp, mv);
-        const int t0 = i.lo + (myg - prefix[mv]) * kTileTokens;
-        const int pg = t0 / p.page;
-        tok = t0 - pg * p.page;
-        hbi = i.hb;
-        phys = __ldg(p.block_table + (int64_t)i.b * p.bt_stride + pg);
-        if ((unsigned)phys >= (unsigned)p.num_blocks) {
-          if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
-          bad = 1;
-          phys = 0;
-        }
-      }
-      const int n = g1 - g < 32 ? g1 - g : 32;
-      for (int i = 0; i < n; ++i, ++it) {
-        const int st = it % nstage;
-        const uint32_t ph = (uint32_t)(it / nstage) & 1u;
-        const int phys_i = __shfl_sync(kFull, phys, i);
-        const int tok_i = __shfl_sync(kFull, tok, i);
-        const int hb_i = __shfl_sync(kFull, hbi, i);
-        const int bad_i = __shfl_sync(kFull, bad, i);
-        int ok = 1;
-        if (lane == 0) {
-          ok = mbar_wait(empty0 + 8 * st, ph ^ 1u, p.status, abort_flag) ? 1 : 0;
-          if (ok) {
-            const uint32_t fb = full0 + 8 * st;
-            const uint32_t dst = stage0 + (uint32_t)st * C::STAGE_BYTES;
-            meta[st] = bad_i;
-            if (bad_i) {
-              mbar_arrive(fb);  // consumers skip the tile
-            } else {
-              mbar_arrive_expect_tx(fb, kTileTx + (SCALED ? 2u * sp.scale_tx_bytes : 0u));
-#pragma unroll
-              for (int c = 0; c < C::NC; ++c) {
-                tma_load_4d(dst + c * C::CHUNK_BYTES, &tm_k, fb, c * C::BOX_ELEMS, tok_i,
-                            hb_i * HB, phys_i);
-                tma_load_4d(dst + C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, fb,
-                            c * C::BOX_ELEMS, tok_i, hb_i * HB, phys_i);
-              }
-              if constexpr (SCALED) {
-                const int64_t so = (int64_t)phys_i * p.sc_sb + (int64_t)tok_i * p.sc_st;
-                bulk_load(dst + 2 * C::TILE_BYTES, p.k_scale + so, sp.scale_tx_bytes, fb);
-                bulk_load(dst + 2 * C::TILE_BYTES + 1024, p.v_scale + so, sp.scale_tx_bytes, fb);
-              }
-            }
-          }
-        }
-        if (!__shfl_sync(kFull, ok, 0)) {
-          aborted = true;
-          break;
-        }
-      }
-    }
-    if (lane == 0 && (aborted || *abort_flag)) {
-      // give the copies still in flight a bounded chance to land before the CTA exits
-      for (int k = 1; k <= nstage && k <= it; ++k) {
-        const int ii = it - k;
-        mbar_wait_slow(full0 + 8 * (ii % nstage), (uint32_t)(ii / nstage) & 1u, nullptr,
-                       abort_flag, false);
-      }
-    }
-    return;
-  }
-
-  // =============================== consumer warps ============================================
-  const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
-  const int hg = HB * p.group;              // query heads of one head block
-  int it = 0;
-  int v = find_vseq(prefix, nv, g0);
-  int g = g0;
-  bool aborted = false;
-
-  while (g < g1 && !aborted) {
-    while (prefix[v + 1] <= g) ++v;
-    const VseqInfo vi = vseq_info(sp, v);
-    const int vend = prefix[v + 1];
-    const int seg_end = g1 < vend ? g1 : vend;
-    int j = g - prefix[v];
-    const bool whole = (j == 0) && (seg_end == vend) && (sp.splits == 1);
-    const int kvh = vi.hb * HB + role;
-
-    // ---- query rows of this kv head's group as B fragments: thread (g, t) holds head g (+8 per
-    // n-tile), head_dim pairs of its k slots; heads >= group are zero --------------------------
-    uint32_t qb[C::KSTEPS][NG][2];
-#pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
-      const int head = 8 * ng + gq;
-      const bool live = head < p.group;
-      const __half* qrow = (const __half*)p.q + (int64_t)vi.b * p.q_sb +
-                           (int64_t)(kvh * p.group + (live ? head : 0)) * p.q_sh;
-#pragma unroll
-      for (int ks = 0; ks < C::KSTEPS; ++ks) {
-        int c_lo, c_hi;  // head_dim index of k slots (2t, 2t+1) and (2t+8, 2t+9)
-        if constexpr (is_16bit(KV)) {
-          c_lo = 16 * ks + 2 * tq;
-          c_hi = c_lo + 8;
-        } else {
-          // 8-bit rows are read as 16-byte chunks 2t and 2t+1; k-step ks uses word ks % 4 of
-          // chunk 2t + ks / 4, whose four elements fill the thread's four k slots
-          c_lo = 32 * tq + 16 * (ks >> 2) + 4 * (ks & 3);
-          c_hi = c_lo + 2;
-        }
-        qb[ks][ng][0] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_lo)) : 0u;
-        qb[ks][ng][1] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_hi)) : 0u;
-      }
-    }
-    // int8 keys are fed to the tensor core as 1152 + x (cvt_pair_biased); the surplus
-    // 1152 * sum_d q[head][d] is removed from the scores of heads 2t and 2t+1 afterwards
-    float qbias[NG][2];
-#pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
-      qbias[ng][0] = qbias[ng][1] = 0.f;
-      if constexpr (KV == PD_KV_I8) {
-        float hs = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < C::KSTEPS; ++ks) {
-          const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][0]));
-          const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][1]));
-          hs += (x.x + x.y) + (y.x + y.y);
-        }
-        hs += __shfl_xor_sync(kFull, hs, 1);
-        hs += __shfl_xor_sync(kFull, hs, 2);  // sum over head_dim of head g
-        qbias[ng][0] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq));
-        qbias[ng][1] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq + 1));
-      }
-    }
-
-    float m[NG][2], l[NG][2];
-    float o[C::MT][NG][4];
-#pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
-      m[ng][0] = m[ng][1] = -INFINITY;
-      l[ng][0] = l[ng][1] = 0.f;
-    }
-#pragma unroll
-    for (int mt = 0; mt < C::MT; ++mt)
-#pragma unroll
-      for (int ng = 0; ng < NG; ++ng) o[mt][ng][0] = o[mt][ng][1] = o[mt][ng][2] = o[mt][ng][3] = 0.f;
-
-    for (; g < seg_end; ++g, ++j, ++it) {
-      const int st = it % nstage;
-      if (!mbar_wait(full0 + 8 * st, (uint32_t)(it / nstage) & 1u, p.status, abort_flag)) {
-        aborted = true;
-        break;
-      }
-      if (meta[st] == 0) {
-        const uint32_t sbase = stage0 + (uint32_t)st * C::STAGE_BYTES;
-        const uint32_t kbase = sbase + role * (kTileTokens * 128);
-        const uint32_t scales = sbase + 2 * C::TILE_BYTES + kvh * 2;
-        const int remaining = vi.hi - (vi.lo + j * kTileTokens);
-        if (remaining >= kTileTokens)
-          consume_tile<KV, D, HB, SCALED, NG, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2,
-                                                     lane, qb, qbias, m, l, o);
-        else
-          consume_tile<KV, D, HB, SCALED, NG, true>(kbase, scales, p.hkv, remaining, p.scale_log2,
-                                                    lane, qb, qbias, m, l, o);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * st);
-    }
-    if (aborted) break;
-
-    // ---- segment epilogue: the thread owns heads 2t, 2t+1 (+8 per n-tile) -----------------------
-    const float unscale = SCALED ? (1.f / 256.f) : 1.f;
-#pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float lsum = l[ng][e];
-#pragma unroll
-        for (int sh = 4; sh < 32; sh <<= 1) lsum += __shfl_xor_sync(kFull, lsum, sh);
-        const int head = 8 * ng + 2 * tq + e;
-        if (head >= p.group) continue;
-        const float inv = lsum > 0.f ? unscale / lsum : 0.f;
-        const float lse = lsum > 0.f ? m[ng][e] + log2f(lsum) : -INFINITY;
-        const int hq = kvh * p.group + head;
-        __half* dst16 = nullptr;
-        float* dst32 = nullptr;
-        if (whole) {
-          if (p.out) dst16 = (__half*)p.out + (int64_t)vi.b * p.o_sb + (int64_t)hq * p.o_sh;
-          if (p.res_o) {
-            dst32 = p.res_o + ((int64_t)vi.b * p.hq + hq) * D;
-            if (gq == 0) p.res_lse[(int64_t)vi.b * p.hq + hq] = lse;
-          }
-        } else {
-          const int64_t slot_row = (int64_t)(w + v) * hg + role * p.group + head;
-          dst32 = p.part_o + slot_row * D;
-          if (gq == 0) p.part_lse[slot_row] = lse;
-        }
-        if constexpr (is_16bit(KV)) {
-          // m-tile mt holds head_dim 16*mt + g (regs 0, 1) and 16*mt + g + 8 (regs 2, 3)
-#pragma unroll
-          for (int mt = 0; mt < C::MT; ++mt) {
-            const float x = o[mt][ng][e] * inv, y = o[mt][ng][2 + e] * inv;
-            const int col = 16 * mt + gq;
-            if (dst16) {
-              store_io<KV>(dst16, col, x);
-              store_io<KV>(dst16, col + 8, y);
-            }
-            if (dst32) {
-              dst32[col] = x;
-              dst32[col + 8] = y;
-            }
-          }
-        } else {
-#pragma unroll
-          for (int jj = 0; jj < D / 32; ++jj) {
-            const float x0 = o[2 * jj][ng][e] * inv, x1 = o[2 * jj][ng][2 + e] * inv;
-            const float x2 = o[2 * jj + 1][ng][e] * inv, x3 = o[2 * jj + 1][ng][2 + e] * inv;
-            const int col = 32 * jj + 4 * gq;
-            if (dst16) {
-              uint2 pk;
-              pk.x = pack_io2<KV>(x0, x1);
-              pk.y = pack_io2<KV>(x2, x3);
-              *reinterpret_cast<uint2*>(dst16 + col) = pk;
-            }
-            if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
-          }
-        }
-      }
-    }
-    if (!whole) {
-      // Ticket: every segment of this (request, kv head) adds one after its partial is visible;
-      // whoever completes the count merges them all.  Nobody waits for anybody.
-      __threadfence();
-      __syncwarp();
-      const int v0 = (vi.hb * p.batch + vi.b) * sp.splits;
-      int* unit_ticket = sp.tickets + (int64_t)vi.b * p.hkv + kvh;
-      // An unsplit request cut over more than kMergeRadix workers (one long request can span
-      // every worker) is merged in two levels: chunks of kMergeRadix consecutive segments
-      // first, each by the warp that completes the chunk, into the chunk's first slot; then
-      // the chunk results by the warp that completes the unit.  The chunk merges of one
-      // request run on different SMs at the same time.
-      int wfirst = 0, nseg = 0;
-      if (sp.splits == 1) {
-        wfirst = prefix[v0] / per;
-        nseg = (prefix[v0 + 1] - 1) / per - wfirst + 1;
-      }
-      if (nseg > kMergeRadix) {
-        const int chunk = (w - wfirst) / kMergeRadix;
-        const int csize = min(kMergeRadix, nseg - chunk * kMergeRadix);
-        const int nchunk = (nseg + kMergeRadix - 1) / kMergeRadix;
-        const int cslot = wfirst + chunk * kMergeRadix + v0;
-        int done = 0;
-        if (lane == 0) {
-          int* chunk_ticket = sp.tickets + (int64_t)p.batch * p.hkv + (int64_t)cslot * HB + role;
-          done = atomicAdd(chunk_ticket, 1) + 1 == csize;
-          if (done) *chunk_ticket = 0;
-        }
-        if (__shfl_sync(kFull, done, 0)) {
-          __threadfence();
-          merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, cslot, csize, 1, cslot);
-          __threadfence();
-          __syncwarp();
-          int last = 0;
-          if (lane == 0) {
-            last = atomicAdd(unit_ticket, 1) + 1 == nchunk;
-            if (last) *unit_ticket = 0;
-          }
-          if (__shfl_sync(kFull, last, 0)) {
-            __threadfence();
-            merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
-                              kMergeRadix, -1);
-          }
-        }
-      } else {
-        int last = 0;
-        if (lane == 0) {
-          int expected = 0;
-          for_each_segment(prefix, per, v0, sp.splits, [&](int) { ++expected; });
-          last = atomicAdd(unit_ticket, 1) + 1 == expected;
-          if (last) *unit_ticket = 0;  // leave the counter as it was found
-        }
-        if (__shfl_sync(kFull, last, 0)) {
-          __threadfence();
-          merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane);
-        }
-      }
-    }
-    ++v;
-  }
-}
 
 // ---------------------------------------------------------------------------------------------
 // host side
@@ -1169,7 +158,23 @@ struct MapKey {
 
 // Tensor map over one cache tensor with dimensions ordered (head_dim, token, head, block) so
 // that a box lands in shared memory as [head][token][128 bytes]: a head's 16 token rows are
-// consecutive 128-byte rows and the 128-byte swizzle spreads them over all banks.
+// consecutive 128-byte rows and the 128-byte swizzle spreads them over all banks.  Encoded
+// straight into caller storage; allocates nothing.
+static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  const int eb = is_16bit(k.kv) ? 2 : 1;
+  const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
+  const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(out, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+             const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same through a small cache keyed by everything the encoding depends on.
 static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
   static std::mutex mu;
   static std::vector<std::pair<MapKey, CUtensorMap>> cache;
@@ -1181,25 +186,10 @@ static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
         return true;
       }
   }
-  EncodeFn enc = encode_fn();
-  if (!enc) return false;
-  const int eb = is_16bit(k.kv) ? 2 : 1;
-  const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
-  const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
-  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUtensorMap m;
-  const CUresult r = enc(&m, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
-                         const_cast<void*>(k.base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (cache.size() >= 64) cache.erase(cache.begin());
-    cache.emplace_back(k, m);
-  }
-  *out = m;
+  if (!encode_tensor_map_in_place(k, out)) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() >= 64) cache.erase(cache.begin());
+  cache.emplace_back(k, *out);
   return true;
 }
 
@@ -1254,119 +244,12 @@ static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& 
   }
 }
 
-int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
-  const Shape s = derive(a);
-  SmemPlan sm;
-  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
-  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
-  if (!a->workspace || a->workspace_bytes < wl.total) return PD_ERR_WORKSPACE;
-
-  MapKey key{a->k_cache, a->kv_stride_block, a->kv_stride_token, a->kv_stride_head, a->head_dim,
-             a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
-  CUtensorMap mk, mv;
-  if (!get_tensor_map(key, &mk)) return PD_ERR_CUDA;
-  key.base = a->v_cache;
-  if (!get_tensor_map(key, &mv)) return PD_ERR_CUDA;
-
-  StreamParams sp;
-  sp.p = p;
-  sp.p.num_splits = s.splits;
-  sp.p.part_lse = (float*)((char*)a->workspace + wl.lse_off);
-  sp.p.part_o = (float*)((char*)a->workspace + wl.o_off);
-  sp.nvseq = s.nvseq;
-  sp.nhb = s.nhb;
-  sp.splits = s.splits;
-  sp.nstage = sm.nstage;
-  sp.wpc = s.wpc;
-  sp.bar_off = sm.bar_off;
-  sp.meta_off = sm.meta_off;
-  sp.misc_off = sm.misc_off;
-  sp.prefix_off = sm.prefix_off;
-  sp.tickets = (int32_t*)((char*)a->workspace + wl.ticket_off);
-  sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
-
-  const cudaStream_t st = (cudaStream_t)a->stream;
-  // the arrival counters of the in-kernel merge start at zero
-  if (cudaMemsetAsync(sp.tickets, 0, wl.ticket_bytes, st) != cudaSuccess) return PD_ERR_CUDA;
-  cudaError_t e;
-  if (a->kv_dtype == PD_KV_F16) {
-    e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 256 ? launch_hb<PD_KV_F16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else if (a->kv_dtype == PD_KV_BF16) {
-    e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else if (a->kv_dtype == PD_KV_E5M2) {
-    e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                 : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else {
-    e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  }
-  return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
-}
-
-// ---------------------------------------------------------------------------------------------
-// pd_decode_static: the streaming decode with its scratch in library-owned device memory
-// ---------------------------------------------------------------------------------------------
-// Scratch of pd_decode_static.  It is part of the loaded module: every GPU that loads this
-// library holds these bytes from load until the process exits.  All calls share it.
-static __device__ __align__(256) unsigned char g_static_scratch[PD_STATIC_SCRATCH_BYTES];
-
-// Device address of g_static_scratch on the current device, looked up once per device.  In host
-// code the array's name is only a handle for the runtime, not an address a kernel can use; the
-// address has to come from cudaGetSymbolAddress with the target device current.
-static void* static_scratch_address() {
-  static std::mutex mu;
-  static void* address[64] = {};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!address[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return nullptr;
-    }
-    address[dev] = ptr;
-  }
-  return address[dev];
-}
-
-// Same tensor map as get_tensor_map builds, encoded straight into caller storage: no cache,
-// so nothing is allocated on the host either.
-static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
-  EncodeFn enc = encode_fn();
-  if (!enc) return false;
-  const int eb = is_16bit(k.kv) ? 2 : 1;
-  const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
-  const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
-  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return enc(out, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
-             const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
-  const Shape s = derive(a);
-  SmemPlan sm;
-  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
-  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
-  if (wl.total > (uint64_t)PD_STATIC_SCRATCH_BYTES) return PD_ERR_TOO_LARGE;
-  char* scratch = (char*)static_scratch_address();
-  if (!scratch) return PD_ERR_CUDA;
-
-  MapKey key{a->k_cache, a->kv_stride_block, a->kv_stride_token, a->kv_stride_head, a->head_dim,
-             a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
-  CUtensorMap mk, mv;
-  if (!encode_tensor_map_in_place(key, &mk)) return PD_ERR_CUDA;
-  key.base = a->v_cache;
-  if (!encode_tensor_map_in_place(key, &mv)) return PD_ERR_CUDA;
-
-  // Only the arrival counters have to start at zero; they are cleared below, on the stream,
-  // before the kernel.  Every partial slot is written before the merge inside the kernel reads it.
+// Fills the kernel's parameter block for scratch at `scratch`, clears the arrival counters on the
+// stream and launches the instantiation that serves the arguments.  Shared by pd_decode and
+// pd_decode_static, which differ only in where the scratch lives and how the tensor maps are made.
+static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s, const SmemPlan& sm,
+                         const WorkspaceLayout& wl, char* scratch, const CUtensorMap& mk,
+                         const CUtensorMap& mv, int sm_count) {
   StreamParams sp;
   sp.p = p;
   sp.p.num_splits = s.splits;
@@ -1405,6 +288,67 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
+static MapKey map_key(const PdDecodeArgs* a, const Shape& s, const void* base) {
+  return MapKey{base, a->kv_stride_block, a->kv_stride_token, a->kv_stride_head, a->head_dim,
+                a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
+}
+
+int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
+  const Shape s = derive(a);
+  SmemPlan sm;
+  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
+  if (!a->workspace || a->workspace_bytes < wl.total) return PD_ERR_WORKSPACE;
+  CUtensorMap mk, mv;
+  if (!get_tensor_map(map_key(a, s, a->k_cache), &mk) || !get_tensor_map(map_key(a, s, a->v_cache), &mv))
+    return PD_ERR_CUDA;
+  return launch_stream(a, p, s, sm, wl, (char*)a->workspace, mk, mv, sm_count);
+}
+
+// ---------------------------------------------------------------------------------------------
+// pd_decode_static: the streaming decode with its scratch in library-owned device memory
+// ---------------------------------------------------------------------------------------------
+// Scratch of pd_decode_static.  It is part of the loaded module: every GPU that loads this
+// library holds these bytes from load until the process exits.  All calls share it.
+static __device__ __align__(256) unsigned char g_static_scratch[PD_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.  In host
+// code the array's name is only a handle for the runtime, not an address a kernel can use; the
+// address has to come from cudaGetSymbolAddress with the target device current.
+static void* static_scratch_address() {
+  static std::mutex mu;
+  static void* address[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    address[dev] = ptr;
+  }
+  return address[dev];
+}
+
+static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
+  const Shape s = derive(a);
+  SmemPlan sm;
+  if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
+  if (wl.total > (uint64_t)PD_STATIC_SCRATCH_BYTES) return PD_ERR_TOO_LARGE;
+  char* scratch = (char*)static_scratch_address();
+  if (!scratch) return PD_ERR_CUDA;
+  // Only the arrival counters have to start at zero; launch_stream clears them on the stream
+  // ahead of the kernel.  Every partial slot is written before the merge inside the kernel
+  // reads it.  The tensor maps are encoded in place: no cache, so nothing is allocated.
+  CUtensorMap mk, mv;
+  if (!encode_tensor_map_in_place(map_key(a, s, a->k_cache), &mk) ||
+      !encode_tensor_map_in_place(map_key(a, s, a->v_cache), &mv))
+    return PD_ERR_CUDA;
+  return launch_stream(a, p, s, sm, wl, scratch, mk, mv, sm_count);
+}
 
 // A wait nobody ends, on purpose: one warp initialises an mbarrier that no thread and no copy
 // ever arrives on and waits for it with the kernel's own bounded wait.  The wait must give up
