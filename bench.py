@@ -217,7 +217,8 @@ def run_ours(args) -> None:
     kv_sharded = args.workload == "c4" and world > 1
     if kv_sharded:
         q, cache = sharding.make_kv_range_shard(args.workload, rank, world, dev, seed=args.seed)
-        runner = sharding.KVRangeShardedDecoder(q, cache, group=dist.group.WORLD, kernel=args.kernel)
+        runner = sharding.KVRangeShardedDecoder(q, cache, group=dist.group.WORLD, kernel=args.kernel,
+                                                exchange=args.exchange)
         for _ in range(2):
             runner.step()
         if not args.no_graph:
@@ -354,7 +355,7 @@ def run_ours(args) -> None:
                    "resident_pool_bytes_per_gpu": resident,
                    "l2": f"inputs ({resident / 1e6:.0f} MB per GPU) exceed the {L2_BYTES >> 20} MB L2"
                          if resident > 2 * L2_BYTES else "inputs fit in L2: latency-bound, no HBM claim",
-                   "parallelism": ("kv-range sharding + all-gather + merge" if kv_sharded
+                   "parallelism": (f"kv-range sharding + {args.exchange} exchange + merge" if kv_sharded
                                    else f"request sharding x{world}, no communication")},
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu_gbs / peak, "peak_kind": f"of {peak_kind}",
@@ -399,6 +400,8 @@ def main() -> None:
     ap.add_argument("--cpu-tokens", type=int, default=40000,
                     help="size of the CPU sample in tokens")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--exchange", choices=("nccl", "peer"), default="nccl",
+                    help="KV-range-sharded runs: NCCL all-gather + merge, or direct peer stores + merge")
     ap.add_argument("--no-graph", action="store_true",
                     help="KV-range-sharded runs: issue the step from the host instead of a CUDA graph")
     ap.add_argument("--pg-timeout", type=int, default=120, help="process-group timeout in seconds")

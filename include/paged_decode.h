@@ -214,6 +214,37 @@ PD_API int pd_merge(const PdMergeArgs* args);
 /* Dense dequantised fp16 gather (see PdGatherArgs). */
 PD_API int pd_gather(const PdGatherArgs* args);
 
+/* Arguments of the peer exchange: the cross-GPU merge of the KV-range-sharded long-context path
+ * done with plain peer stores instead of a collective library.  Nothing in the reference
+ * corresponds to it (the reference is single-GPU); the merge arithmetic is that of
+ * _split_reduce_kernel (pagedattn/triton_decode.py:221-240) over ranks.  Every rank owns one
+ * exchange buffer of pd_exchange_bytes() bytes, zero-filled once, mapped into every peer
+ * (e.g. torch symmetric memory); `peer_bufs[r]` is rank r's buffer as seen from this rank. */
+typedef struct PdExchangeArgs {
+  void* const* peer_bufs;  /* host array [world]; entry [rank] is this rank's own buffer */
+  int32_t world, rank;     /* world <= 16 */
+  const float* local;      /* this rank's partial: rows*head_dim normalised fp32 results, then
+                              rows base-2 log-sum-exps (what pd_decode's result_f32/result_lse
+                              give when they point into one buffer) */
+  int32_t rows, head_dim, rows_per_batch; /* rows = batch * num_q_heads; rows_per_batch = num_q_heads */
+  void* out;               /* [batch, num_q_heads, head_dim] io_dtype, strides below; may be NULL */
+  int64_t out_stride_b, out_stride_h;
+  int32_t io_dtype;
+  float* result_f32;       /* optional merged fp32 result [rows, head_dim] */
+  float* result_lse;       /* optional merged lse [rows] */
+  uint32_t* status;        /* optional device word: PD_DEV_TIMEOUT if a peer's partial did not
+                              arrive within one second (the merge is then skipped) */
+  void* stream;
+} PdExchangeArgs;
+
+/* Bytes of one rank's exchange buffer (256-byte aligned base expected). */
+PD_API uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim);
+
+/* One exchange step: store `local` into every rank's buffer (this rank's own included), raise
+ * the flags, then merge the `world` partials that land in this rank's buffer into `out`.  Two
+ * kernel launches on `stream`; all ranks must call it once per step. */
+PD_API int pd_exchange_step(const PdExchangeArgs* args);
+
 /* Failure-path self-test with no counterpart in the reference: runs the kernels' bounded
  * mbarrier wait on a barrier nothing ever completes.  After `limit_ns` (at most one second) the
  * wait gives up, ORs PD_DEV_TIMEOUT into *status (a device word) and the kernel returns

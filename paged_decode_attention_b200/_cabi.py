@@ -80,6 +80,15 @@ class PdCacheWriteArgs(ctypes.Structure):
     ]
 
 
+class PdExchangeArgs(ctypes.Structure):
+    _fields_ = [
+        ("peer_bufs", ctypes.POINTER(_c_vp)), ("world", _c_i32), ("rank", _c_i32),
+        ("local", _c_vp), ("rows", _c_i32), ("head_dim", _c_i32), ("rows_per_batch", _c_i32),
+        ("out", _c_vp), ("out_stride_b", _c_i64), ("out_stride_h", _c_i64), ("io_dtype", _c_i32),
+        ("result_f32", _c_vp), ("result_lse", _c_vp), ("status", _c_vp), ("stream", _c_vp),
+    ]
+
+
 class PdGatherArgs(ctypes.Structure):
     _fields_ = [("cache", ctypes.POINTER(PdDecodeArgs)), ("k_dense", _c_vp), ("v_dense", _c_vp),
                 ("s_max", _c_i32)]
@@ -87,7 +96,8 @@ class PdGatherArgs(ctypes.Structure):
 
 EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
            "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather",
-           "pd_decode_static", "pd_cache_write", "pd_selftest_bounded_wait")
+           "pd_decode_static", "pd_cache_write", "pd_selftest_bounded_wait", "pd_exchange_bytes",
+           "pd_exchange_step")
 
 STATIC_SCRATCH_BYTES = 8 << 20
 ERR_TOO_LARGE = -5
@@ -130,6 +140,10 @@ def load() -> ctypes.CDLL:
     lib.pd_merge.argtypes = [ctypes.POINTER(PdMergeArgs)]
     lib.pd_gather.restype = ctypes.c_int
     lib.pd_gather.argtypes = [ctypes.POINTER(PdGatherArgs)]
+    lib.pd_exchange_bytes.restype = _c_u64
+    lib.pd_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32]
+    lib.pd_exchange_step.restype = ctypes.c_int
+    lib.pd_exchange_step.argtypes = [ctypes.POINTER(PdExchangeArgs)]
     lib.pd_selftest_bounded_wait.restype = ctypes.c_int
     lib.pd_selftest_bounded_wait.argtypes = [_c_vp, _c_u64, _c_vp]
     lib.pd_cache_write.restype = ctypes.c_int

@@ -6,6 +6,7 @@
 
 #include "pd_common.cuh"
 #include "pd_cache_write.cuh"
+#include "pd_exchange.cuh"
 #include "pd_merge.cuh"
 #include "pd_simple.cuh"
 #include "pd_stream.h"
@@ -432,6 +433,45 @@ int pd_cache_write(const PdCacheWriteArgs* a) {
     default: PD_CW_D(PD_KV_I8, false) break;
   }
 #undef PD_CW_D
+  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
+
+uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim) {
+  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0) return 0;
+  return exchange_bytes(world, (int64_t)rows * (head_dim + 1));
+}
+
+int pd_exchange_step(const PdExchangeArgs* a) {
+  if (!a || !a->peer_bufs || !a->local) return PD_ERR_INVALID_ARG;
+  if (a->world <= 0 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) return PD_ERR_INVALID_ARG;
+  if (a->rows <= 0 || a->head_dim <= 0 || a->rows_per_batch <= 0) return PD_ERR_INVALID_ARG;
+  if (!a->out && !a->result_f32) return PD_ERR_INVALID_ARG;
+  if (a->io_dtype != PD_IO_F16 && a->io_dtype != PD_IO_BF16) return PD_ERR_INVALID_ARG;
+  if (!aligned(a->local, 16)) return PD_ERR_UNSUPPORTED;
+  PeerPointers peers;
+  for (int r = 0; r < kMaxRanks; ++r) peers.buf[r] = nullptr;
+  for (int r = 0; r < a->world; ++r) {
+    if (!a->peer_bufs[r] || !aligned(a->peer_bufs[r], 256)) return PD_ERR_INVALID_ARG;
+    peers.buf[r] = (unsigned char*)a->peer_bufs[r];
+  }
+  const int64_t n = (int64_t)a->rows * (a->head_dim + 1);
+  const cudaStream_t st = (cudaStream_t)a->stream;
+  exchange_push_kernel<<<a->world, 256, 0, st>>>(a->local, peers, a->world, a->rank, n);
+  if (cudaGetLastError() != cudaSuccess) return PD_ERR_CUDA;
+  ExchangeMergeParams m;
+  m.buf = peers.buf[a->rank];
+  m.world = a->world;
+  m.rows = a->rows;
+  m.d = a->head_dim;
+  m.rows_per_batch = a->rows_per_batch;
+  m.out = a->out;
+  m.dst_sb = a->out_stride_b;
+  m.dst_sh = a->out_stride_h;
+  m.res_o = a->result_f32;
+  m.res_lse = a->result_lse;
+  m.status = a->status;
+  if (a->io_dtype == PD_IO_BF16) exchange_merge_kernel<true><<<a->rows, 128, 0, st>>>(m);
+  else exchange_merge_kernel<false><<<a->rows, 128, 0, st>>>(m);
   return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 

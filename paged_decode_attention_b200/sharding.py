@@ -78,6 +78,63 @@ def make_kv_range_shard(name: str, rank: int, world: int, device, seed: int = 0,
     return q, cache
 
 
+class PeerExchange:
+    """Cross-rank merge of decode partials by direct peer stores (``pd_exchange_step``).
+
+    Every rank owns one exchange buffer in torch symmetric memory, mapped into all peers.  A
+    step stores this rank's flat partial (fp32 results then lses) into every rank's buffer over
+    NVLink, raises a flag there, and merges the partials that arrive in its own buffer: two
+    small kernels of this library instead of an NCCL all-gather plus a merge.  Plain peer
+    stores only — no multicast, nothing is loaded from a peer's memory — and the wait for the
+    flags is bounded (``PD_DEV_TIMEOUT`` in ``status`` after one second).
+    """
+
+    def __init__(self, local: torch.Tensor, out: torch.Tensor, group, status: torch.Tensor | None = None):
+        import ctypes
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _cabi
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # peer stores only
+        b, hq, d = out.shape
+        if local.numel() != b * hq * (d + 1) or local.dtype != torch.float32 or not local.is_contiguous():
+            raise ValueError("local must be the flat fp32 partial: B*Hq*D results then B*Hq lses")
+        if not out.is_contiguous():
+            raise ValueError("out must be contiguous")
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        nbytes = int(_cabi.load().pd_exchange_bytes(self.world, b * hq, d))
+        if nbytes == 0:
+            raise ValueError("exchange supports at most 16 ranks")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=local.device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        torch.cuda.synchronize(local.device)
+        dist.barrier(group)  # every buffer is zero before anybody pushes
+        self._ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+        a = _cabi.PdExchangeArgs()
+        a.peer_bufs = ctypes.cast(self._ptrs, ctypes.POINTER(ctypes.c_void_p))
+        a.world, a.rank = self.world, self.rank
+        a.local = local.data_ptr()
+        a.rows, a.head_dim, a.rows_per_batch = b * hq, d, hq
+        a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), hq * d, d
+        a.io_dtype = _cabi.IO_CODE[out.dtype]
+        if status is not None:
+            a.status = status.data_ptr()
+        self._keep = (local, out, status)
+        self.args, self._ref, self._fn = a, ctypes.byref(a), _cabi.load().pd_exchange_step
+        self.device = local.device
+
+    def step(self) -> None:
+        from . import _cabi
+
+        self.args.stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(self._ref)
+        if rc != 0:
+            _cabi.check(rc, "pd_exchange_step")
+
+
 class KVRangeShardedDecoder:
     """Decode step of one rank of a KV-range-sharded group.
 
@@ -88,7 +145,10 @@ class KVRangeShardedDecoder:
     """
 
     def __init__(self, q: torch.Tensor, cache: PagedKVCache, group=None, kernel: str = "auto",
-                 decode_fn: Callable | None = None, merge_fn: Callable | None = None):
+                 decode_fn: Callable | None = None, merge_fn: Callable | None = None,
+                 exchange: str = "nccl", status: torch.Tensor | None = None):
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' (all-gather + merge) or 'peer' (direct peer stores)")
         self.q, self.cache, self.group, self.kernel = q, cache, group, kernel
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         b, hq, d = q.shape
@@ -110,9 +170,16 @@ class KVRangeShardedDecoder:
             merge_fn = lambda *_: merge_step.step()
         self.decode_fn, self.merge_fn = decode_fn, merge_fn
         self.launches_per_step = 2  # decode (merges its own splits), the cross-rank merge
+        self.peer = None
+        if exchange == "peer" and self.world > 1:
+            self.peer = PeerExchange(self.local, self.out, group, status=status)
+            self.launches_per_step = 3  # decode, push, wait-and-merge
 
     def _run(self) -> None:
         self.decode_fn(self.q, self.cache, self.f32, self.lse, self.kernel)
+        if self.peer is not None:
+            self.peer.step()
+            return
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered.view(-1), self.local, group=self.group)
         else:
