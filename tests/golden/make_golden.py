@@ -1,6 +1,6 @@
 """Produce tests/golden/golden_v1.npz by running the UNMODIFIED reference on the CPU.
 
-Usage:  python tests/golden/make_golden.py [--ref /path/to/paged-decode-attention]
+Usage:  python tests/golden/make_golden.py --ref /path/to/paged-decode-attention
 
 The reference tree is imported, never copied.  For every case of cases.CASES the file
 stores what the reference computes on the seeded inputs of cases.build():
@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import hashlib
+import os
 import pathlib
 import sys
 
@@ -65,9 +66,12 @@ def _ref_cache(ref, case: cases.Case, oc):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("PAGEDATTN_REF"),
+                    help="checkout of the reference project (or set PAGEDATTN_REF)")
     ap.add_argument("--out", default=str(HERE / "golden_v1.npz"))
     args = ap.parse_args()
+    if not args.ref:
+        ap.error("give --ref or set PAGEDATTN_REF to the reference checkout")
     sys.path.insert(0, args.ref)
     import pagedattn as ref  # the reference package, unmodified
     from pagedattn.cache import dequantize_kv, quantize_kv
