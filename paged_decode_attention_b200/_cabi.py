@@ -161,10 +161,6 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what} failed: {status_string(rc)} ({rc})")
 
 
-def _ptr(t: torch.Tensor | None):
-    return None if t is None else t.data_ptr()
-
-
 def _current_stream(device: torch.device):
     if device.type != "cuda":
         return None

@@ -28,7 +28,6 @@ def _worker(rank: int, world: int, port: int, out_path: str):
 
     import torch.distributed as dist
 
-    import paged_decode_attention_b200 as pda
     from paged_decode_attention_b200 import sharding
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -72,7 +71,6 @@ def test_kv_range_sharding_on_two_gpus(tmp_path):
     import torch.multiprocessing as mp
 
     from oracle import adapters, c_oracle
-    import paged_decode_attention_b200 as pda
     from paged_decode_attention_b200 import sharding
 
     world, path = 2, str(tmp_path / "r0.pt")

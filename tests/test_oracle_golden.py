@@ -7,8 +7,6 @@ gather_contiguous's bits on the same seeded inputs.
 
 from __future__ import annotations
 
-import hashlib
-
 import numpy as np
 import pytest
 
