@@ -330,3 +330,45 @@ def test_bounded_wait_gives_up_and_leaves_the_context_usable():
     q_np, oc = cases.build(case)
     out = pda.paged_decode(torch.from_numpy(q_np).cuda(), helpers.to_device_cache(oc))
     helpers.assert_close(out, c_oracle.decode(q_np.astype(np.float32), oc), what="after timeout")
+
+
+def _random_case(seed: int) -> tuple[cases.Case, int | None]:
+    rng = np.random.Generator(np.random.PCG64(seed))
+    kv_dtype = ["fp16", "fp16", "int8", "fp8_e5m2", "bf16"][seed % 5]
+    d = 128 if kv_dtype in ("int8", "fp8_e5m2") else int(rng.choice([64, 128, 256]))
+    hkv = int(rng.choice([1, 2, 3, 4, 8]))
+    group = int(rng.choice([1, 2, 4, 5, 7, 8, 12]))
+    page = int(rng.choice([16, 32, 64]))
+    b = int(rng.integers(1, 40))
+    kind = seed % 3
+    if kind == 0:    # many short requests, some empty
+        lens = rng.integers(0, 70, size=b)
+    elif kind == 1:  # ragged with a long tail
+        lens = np.clip(np.rint(np.exp(np.log(200) + 1.3 * rng.standard_normal(b))), 0, 6000)
+    else:            # a few long requests
+        lens = rng.integers(1000, 9000, size=min(b, 5))
+    splits = [None, None, 1, 2, 5][int(rng.integers(0, 5))]
+    scaled = True if kv_dtype == "int8" else bool(rng.integers(0, 2)) if kv_dtype == "fp8_e5m2" else None
+    case = cases.Case(f"rand{seed}", hkv * group, hkv, d, page, kv_dtype, tuple(int(n) for n in lens), seed=1000 + seed,
+                      scaled=scaled, scale_kind="uniform" if kv_dtype == "fp8_e5m2" else "quant",
+                      io_dtype="bf16" if kv_dtype == "bf16" else "fp16", slack=int(rng.integers(0, 9)))
+    return case, splits
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_random_batches_match_the_oracle(seed):
+    """Seeded random geometry: head counts, groups, page sizes, dtypes, length distributions
+    (empty requests, long tails, few long requests) and split counts, both kernels."""
+    case, splits = _random_case(seed)
+    if sum(case.lens) == 0:
+        pytest.skip("degenerate draw")
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    for kernel in ("auto", "simple"):
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = pda.paged_decode(q, cache, num_splits=splits, kernel=kernel, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        helpers.assert_close(out, ref, bf16=case.io_dtype == "bf16", what=f"{case.name}/{kernel}/{splits}")
