@@ -50,6 +50,7 @@ __host__ __device__ constexpr bool is_16bit(int kv) { return kv == PD_KV_F16 || 
 constexpr int kMaxVseq = 4096;
 constexpr int kMinTilesPerWorker = 4;
 constexpr int kMergeRadix = 8;
+constexpr int kWholeTiles = 16;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxStages = 12;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
@@ -684,11 +685,13 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
     fence_proxy_async();
   }
   __syncthreads();
+  volatile int* longest = abort_flag + 1;  // most tiles any virtual sequence has
   if (warp == 0) {
-    int carry = 0;
+    int carry = 0, most = 0;
     for (int first = 1; first <= nv; first += 32) {
       const int idx = first + lane;
       int x = idx <= nv ? prefix[idx] : 0;
+      most = max(most, x);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int y = __shfl_up_sync(kFull, x, o);
@@ -697,6 +700,9 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
       if (idx <= nv) prefix[idx] = x + carry;
       carry += __shfl_sync(kFull, x, 31);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(kFull, most, o));
+    if (lane == 0) *longest = most;
   }
   __syncthreads();
 
@@ -706,8 +712,16 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
   if (per < kMinTilesPerWorker) per = kMinTilesPerWorker;
   const int w = blockIdx.x * WPC + wl;  // global worker id
   const long long g0l = (long long)w * per;
-  const int g0 = g0l < total ? (int)g0l : total;
-  const int g1 = g0 + per < total ? g0 + per : total;
+  int g0 = g0l < total ? (int)g0l : total;
+  int g1 = g0 + per < total ? g0 + per : total;
+  // A small batch of short requests (fewer virtual sequences than workers, none longer than
+  // kWholeTiles tiles) is dealt out whole, one request per worker, spread over the CTAs first:
+  // every output row is then written directly, with no partial, ticket or merge on the way.
+  if (sp.splits == 1 && nv <= workers && *longest <= kWholeTiles) {
+    const int mine = wl * gridDim.x + blockIdx.x;
+    g0 = mine < nv ? prefix[mine] : total;
+    g1 = mine < nv ? prefix[mine + 1] : total;
+  }
   if (blockIdx.x == 0) {
     // requests without a single token are nobody's work: their rows are zero, their lse -inf
     for (int u = tid; u < sp.nhb * p.batch; u += kThreads) {
