@@ -60,12 +60,15 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, enabled: bool = True):
         self.gpu = gpu_index
+        self.enabled = enabled  # only the reporting rank samples
         self.lines: list[str] = []
         self.proc = None
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
@@ -278,7 +281,7 @@ def run_ours(args) -> None:
     # ---- device-timed region: K steps, CUDA events on the launching stream -------------
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local, enabled=rank == 0) as clocks:
         t_wall0 = time.perf_counter()
         for i in range(args.steps):
             starts[i].record()
