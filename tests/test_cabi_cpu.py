@@ -129,3 +129,16 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_cabi, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(_cabi.NativeLibraryError):
         _cabi.load()
+
+
+def test_header_is_plain_c():
+    """The boundary is a C ABI: the header must compile as C99 with no C++ or CUDA in sight."""
+    import shutil
+    import subprocess
+
+    gcc = "/usr/bin/gcc" if pathlib.Path("/usr/bin/gcc").exists() else shutil.which("gcc")
+    if not gcc:
+        pytest.skip("no C compiler")
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c",
+                        str(ROOT / "include" / "paged_decode.h")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
