@@ -12,6 +12,7 @@ import pathlib
 import shutil
 import subprocess
 import sys
+import time
 
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
@@ -40,6 +41,7 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if not force and not needs_build():
         return LIB
+    started = time.time()
     objs = []
     tmp = PKG / "build"
     tmp.mkdir(exist_ok=True)
@@ -58,6 +60,9 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
             raise RuntimeError(f"nvcc failed on {src}")
     link = [_nvcc(), "-shared", "-o", str(LIB), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(link, check=True)
+    # date the library at the start of the build: a source edited while the compiler ran is then
+    # newer than the library, and the next call rebuilds instead of trusting a stale file
+    os.utime(LIB, (started, started))
     return LIB
 
 

@@ -30,9 +30,10 @@ struct Shape {
 static Shape derive(const PdDecodeArgs* a) {
   Shape s;
   s.hb = head_block(a->num_kv_heads);
-  // head_dim 256 at 16 bits: a stage of 8 consumer warps' worth would be 128 KB, so at most
-  // four heads per block and four consumer warps per CTA (three 64 KB stages)
-  const bool wide = a->head_dim * (is_16bit(a->kv_dtype) ? 2 : 1) == 512;
+  // head_dim 256: a consumer thread holds 64 accumulator and 32 query registers per n-tile, and
+  // at 16 bits a stage of 8 consumer warps' worth would be 128 KB; so at most four heads per
+  // block and four consumer warps per CTA
+  const bool wide = a->head_dim == 256;
   if (wide && s.hb > 4) s.hb = 4;
   s.nhb = a->num_kv_heads / s.hb;
   s.wpc = wide ? 4 / s.hb : base_workers_per_cta(s.hb);
@@ -76,7 +77,9 @@ int stream_supports(const PdDecodeArgs* a) {
   if ((a->kv_dtype == PD_KV_BF16) != (a->io_dtype == PD_IO_BF16)) return PD_ERR_UNSUPPORTED;
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   const int rowb = a->head_dim * eb;
-  if (rowb != 128 && rowb != 256 && !(rowb == 512 && eb == 2)) return PD_ERR_UNSUPPORTED;
+  // 16-bit pages: head_dim 64, 128, 256; 8-bit pages: 128, 256 (rows of whole 128-byte pieces)
+  if (rowb != 128 && rowb != 256 && rowb != 512) return PD_ERR_UNSUPPORTED;
+  if (a->head_dim > 256) return PD_ERR_UNSUPPORTED;
   if (a->batch <= 0) return PD_ERR_UNSUPPORTED;
   const int group = a->num_q_heads / a->num_kv_heads;
   if (group > 16) return PD_ERR_UNSUPPORTED;
@@ -280,10 +283,15 @@ static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s,
         : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                            : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
-    e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                 : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+    if (a->head_dim == 128)
+      e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                   : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+    else
+      e = s.scaled ? launch_hb<PD_KV_E5M2, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                   : launch_hb<PD_KV_E5M2, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else {
-    e = launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+    e = a->head_dim == 128 ? launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_I8, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   }
   return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }

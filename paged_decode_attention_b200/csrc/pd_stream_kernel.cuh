@@ -344,12 +344,13 @@ __device__ __forceinline__ void consume_tile(
       for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
     }
   } else {
-    // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each row give
-    // eight words, word i of chunk jh feeding k-step 4*jh + i
+    // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each 128-byte
+    // piece c of the row give eight words, word i of chunk jh feeding k-step 8*c + 4*jh + i
     const uint32_t row0 = kbase + gq * 128, row1 = row0 + 8 * 128;
 #pragma unroll
-    for (int jh = 0; jh < 2; ++jh) {
-      const uint32_t ch = (uint32_t)((2 * tq + jh) ^ (gq & 7)) << 4;
+    for (int cj = 0; cj < 2 * C::NC; ++cj) {
+      const int c = cj >> 1, jh = cj & 1;
+      const uint32_t ch = (uint32_t)c * C::CHUNK_BYTES + ((uint32_t)((2 * tq + jh) ^ (gq & 7)) << 4);
       uint32_t w0[4], w1[4];
       lds128(row0 + ch, w0);
       lds128(row1 + ch, w1);
@@ -369,7 +370,7 @@ __device__ __forceinline__ void consume_tile(
           a[3] = cvt_pair<KV>(w1[i], true);
         }
 #pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * jh + i][ng][0], qb[4 * jh + i][ng][1]);
+        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
       }
     }
   }
@@ -478,8 +479,9 @@ __device__ __forceinline__ void consume_tile(
       uint32_t r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int chunk = 2 * jj + (gq >> 2);
-        r[k] = lds32(vbase + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) + ((gq & 3) << 2));
+        const int chunk = ((2 * jj) & 7) + (gq >> 2);  // within 128-byte piece jj / 4 of the row
+        r[k] = lds32(vbase + (jj >> 2) * C::CHUNK_BYTES + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) +
+                     ((gq & 3) << 2));
         if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
       }
       // bytes (c0, c2) and (c1, c3) of the token pairs side by side
@@ -849,9 +851,10 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
           c_lo = 16 * ks + 2 * tq;
           c_hi = c_lo + 8;
         } else {
-          // 8-bit rows are read as 16-byte chunks 2t and 2t+1; k-step ks uses word ks % 4 of
-          // chunk 2t + ks / 4, whose four elements fill the thread's four k slots
-          c_lo = 32 * tq + 16 * (ks >> 2) + 4 * (ks & 3);
+          // every 128-byte piece of an 8-bit row is read as its 16-byte chunks 2t and 2t+1;
+          // k-step ks uses word ks % 4 of chunk 2t + (ks / 4) % 2 of piece ks / 8, whose four
+          // elements fill the thread's four k slots
+          c_lo = 128 * (ks >> 3) + 32 * tq + 16 * ((ks >> 2) & 1) + 4 * (ks & 3);
           c_hi = c_lo + 2;
         }
         qb[ks][ng][0] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_lo)) : 0u;

@@ -208,6 +208,38 @@ def test_head_dim_256(hq, hkv, io, kernel):
         helpers.assert_close(_run(case, kernel, splits), ref, bf16=io == "bf16", what=f"D256 {hq}/{hkv} {io}")
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("hq,hkv,kv,scaled", [(16, 4, "int8", True), (8, 1, "fp8_e5m2", False),
+                                              (24, 2, "fp8_e5m2", True), (32, 8, "int8", True),
+                                              (36, 3, "int8", True)])
+def test_head_dim_256_on_8bit_pages(hq, hkv, kv, scaled, kernel):
+    """Rows of two 128-byte pieces on 8-bit pages: both kernels, with and without scales,
+    groups on one and on two n-tiles, a masked last tile, a one-token request."""
+    case = cases.Case("d256q", hq, hkv, 256, 16, kv, (700, 33, 2100, 1), seed=59, scaled=scaled,
+                      scale_kind="uniform" if kv == "fp8_e5m2" else "quant")
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    if kernel == "stream":
+        cache = helpers.to_device_cache(oc)
+        q = helpers.q_to_device(case, q_np)
+        assert pdec.selected_kernel(pdec.build_args(q, cache, torch.empty_like(q))) == "stream"
+    for splits in (None, 3):
+        helpers.assert_close(_run(case, kernel, splits), ref, what=f"D256 {hq}/{hkv} {kv}")
+
+
+@pytest.mark.parametrize("kv", ["int8", "fp8_e5m2"])
+def test_8bit_pages_with_narrow_rows_take_the_general_kernel(kv):
+    """head_dim 64 on 8-bit pages is a 64-byte row, which the streaming kernel does not serve:
+    `auto` must pick the general kernel and still match."""
+    case = cases.Case("d64q", 14, 2, 64, 16, kv, (150, 17, 64), seed=61)
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    assert pdec.selected_kernel(pdec.build_args(q, cache, torch.empty_like(q))) == "simple"
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    helpers.assert_close(_run(case, "auto", None), ref, what=f"D64 {kv}")
+
+
 def test_merge_partials_matches_oracle():
     rng = np.random.Generator(np.random.PCG64(77))
     po_ = rng.standard_normal((5, 3, 14, 64), dtype=np.float32)
