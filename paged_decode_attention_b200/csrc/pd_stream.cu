@@ -43,8 +43,8 @@ static Shape derive(const PdDecodeArgs* a) {
   s.scaled = a->k_scale != nullptr;
   if (s.hb == 8 && !is_16bit(a->kv_dtype) && nv >= 64) s.wpc = 2;
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
-  const int nc = a->head_dim * eb / 128;
-  s.stage_bytes = 2 * nc * s.hb * kTileTokens * 128 + (s.scaled ? 2048 : 0);
+  // a tile of K (or V) is hb heads x 16 tokens x the row, whatever pieces the row is moved in
+  s.stage_bytes = 2 * s.hb * kTileTokens * a->head_dim * eb + (s.scaled ? 2048 : 0);
   s.threads = s.wpc * (s.hb + 1) * 32;
   return s;
 }
@@ -77,8 +77,9 @@ int stream_supports(const PdDecodeArgs* a) {
   if ((a->kv_dtype == PD_KV_BF16) != (a->io_dtype == PD_IO_BF16)) return PD_ERR_UNSUPPORTED;
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   const int rowb = a->head_dim * eb;
-  // 16-bit pages: head_dim 64, 128, 256; 8-bit pages: 128, 256 (rows of whole 128-byte pieces)
-  if (rowb != 128 && rowb != 256 && rowb != 512) return PD_ERR_UNSUPPORTED;
+  // rows of 64 bytes or of whole 128-byte pieces: head_dim 32..256 on 16-bit pages, 64..256
+  // on 8-bit pages
+  if (rowb != 64 && rowb != 128 && rowb != 256 && rowb != 512) return PD_ERR_UNSUPPORTED;
   if (a->head_dim > 256) return PD_ERR_UNSUPPORTED;
   if (a->batch <= 0) return PD_ERR_UNSUPPORTED;
   const int group = a->num_q_heads / a->num_kv_heads;
@@ -101,7 +102,10 @@ int stream_supports(const PdDecodeArgs* a) {
   if ((long long)s.nhb * a->batch * s.splits > kMaxVseq) return PD_ERR_UNSUPPORTED;
   SmemPlan sm;
   if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
-  // tensor-map limits
+  // tensor-map limits: 16-byte aligned base and strides, strides below 2^40 bytes
+  if (((uintptr_t)a->k_cache % 16) || ((uintptr_t)a->v_cache % 16) || (a->kv_stride_block * eb) % 16 ||
+      (a->kv_stride_token * eb) % 16 || (a->kv_stride_head * eb) % 16)
+    return PD_ERR_UNSUPPORTED;
   if ((uint64_t)a->kv_stride_block * eb >= (1ull << 40) || (uint64_t)a->kv_stride_token * eb >= (1ull << 40) ||
       (uint64_t)a->kv_stride_head * eb >= (1ull << 40))
     return PD_ERR_UNSUPPORTED;
@@ -160,8 +164,9 @@ struct MapKey {
 };
 
 // Tensor map over one cache tensor with dimensions ordered (head_dim, token, head, block) so
-// that a box lands in shared memory as [head][token][128 bytes]: a head's 16 token rows are
-// consecutive 128-byte rows and the 128-byte swizzle spreads them over all banks.  Encoded
+// that a box lands in shared memory as [head][token][128 bytes] (64 bytes when that is the
+// whole row): a head's 16 token rows are consecutive rows and the swizzle of the row's width
+// spreads them over all banks.  Encoded
 // straight into caller storage; allocates nothing.
 static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
   EncodeFn enc = encode_fn();
@@ -169,11 +174,13 @@ static bool encode_tensor_map_in_place(const MapKey& k, CUtensorMap* out) {
   const int eb = is_16bit(k.kv) ? 2 : 1;
   const cuuint64_t dims[4] = {(cuuint64_t)k.d, (cuuint64_t)k.page, (cuuint64_t)k.hkv, (cuuint64_t)k.nb};
   const cuuint64_t strides[3] = {(cuuint64_t)k.st * eb, (cuuint64_t)k.sh * eb, (cuuint64_t)k.sb * eb};
-  const cuuint32_t box[4] = {(cuuint32_t)(128 / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
+  const int pitch = k.d * eb < 128 ? k.d * eb : 128;
+  const cuuint32_t box[4] = {(cuuint32_t)(pitch / eb), (cuuint32_t)kTileTokens, (cuuint32_t)k.hb, 1u};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return enc(out, k.kv == PD_KV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
              const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             pitch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -277,21 +284,27 @@ static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s,
   if (a->kv_dtype == PD_KV_F16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
         : a->head_dim == 256 ? launch_hb<PD_KV_F16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+        : a->head_dim == 64 ? launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                          : launch_hb<PD_KV_F16, 32, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_BF16) {
     e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
         : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+        : a->head_dim == 64 ? launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                          : launch_hb<PD_KV_BF16, 32, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else if (a->kv_dtype == PD_KV_E5M2) {
     if (a->head_dim == 128)
       e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                    : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-    else
+    else if (a->head_dim == 256)
       e = s.scaled ? launch_hb<PD_KV_E5M2, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
                    : launch_hb<PD_KV_E5M2, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+    else
+      e = s.scaled ? launch_hb<PD_KV_E5M2, 64, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                   : launch_hb<PD_KV_E5M2, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   } else {
     e = a->head_dim == 128 ? launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_I8, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+        : a->head_dim == 256 ? launch_hb<PD_KV_I8, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
+                           : launch_hb<PD_KV_I8, 64, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
   }
   return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }

@@ -66,11 +66,14 @@ template <int KV, int D, int HB, bool SCALED>
 struct StreamCfg {
   static constexpr int EB = is_16bit(KV) ? 2 : 1;
   static constexpr int ROWB = D * EB;
-  static_assert(ROWB == 128 || ROWB == 256 || ROWB == 512, "row must be 1, 2 or 4 128-byte chunks");
-  static constexpr int NC = ROWB / 128;                     // 128-byte chunks per row
-  static constexpr int BOX_ELEMS = 128 / EB;                // elements of one chunk
+  static_assert(ROWB == 64 || ROWB == 128 || ROWB == 256 || ROWB == 512,
+                "a row is 64 bytes or 1, 2 or 4 pieces of 128 bytes");
+  static constexpr int PITCH = ROWB < 128 ? ROWB : 128;     // bytes of one shared-memory row
+  static constexpr int CPR = PITCH / 16;                    // 16-byte chunks per shared-memory row
+  static constexpr int NC = ROWB / PITCH;                   // pieces (TMA boxes) per row
+  static constexpr int BOX_ELEMS = PITCH / EB;              // elements of one piece
   static constexpr int WARPS_PER_WORKER = HB + 1;
-  static constexpr int CHUNK_BYTES = HB * kTileTokens * 128; // one TMA box
+  static constexpr int CHUNK_BYTES = HB * kTileTokens * PITCH; // one TMA box
   static constexpr int TILE_BYTES = NC * CHUNK_BYTES;        // K (or V) of one tile
   static constexpr int SCALE_BYTES = SCALED ? 2048 : 0;      // K scales at +0, V scales at +1024
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES + SCALE_BYTES;
@@ -85,6 +88,15 @@ struct StreamParams {
   int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
   uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
 };
+
+// Where the TMA swizzle puts 16-byte chunk `chunk` of token row `token`: the 128-byte mode
+// XORs the chunk index with the row index mod 8, the 64-byte mode (64-byte rows, four chunks)
+// with bits 1-2 of the row index.
+template <int PITCH>
+__device__ __forceinline__ int swizzled_chunk(int chunk, int token) {
+  if constexpr (PITCH == 128) return chunk ^ (token & 7);
+  else return chunk ^ ((token >> 1) & 3);
+}
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -334,23 +346,26 @@ __device__ __forceinline__ void consume_tile(
     // lo/hi are the two 16-byte chunks of the k-step
     const int mi = lane >> 3;
     const int token = 8 * (mi & 1) + (lane & 7);
-    const uint32_t row = kbase + token * 128;
+    const uint32_t row = kbase + token * C::PITCH;
 #pragma unroll
     for (int ks = 0; ks < C::KSTEPS; ++ks) {
-      const int chunk = ((2 * ks) & 7) + (mi >> 1);
+      const int chunk = ((2 * ks) % C::CPR) + (mi >> 1);
       uint32_t a[4];
-      ldmatrix_x4(row + (ks >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
+      ldmatrix_x4(row + ((2 * ks) / C::CPR) * C::CHUNK_BYTES + (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
 #pragma unroll
       for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
     }
   } else {
-    // tokens g and g + 8 share the swizzle phase; 16-byte chunks 2t and 2t+1 of each 128-byte
-    // piece c of the row give eight words, word i of chunk jh feeding k-step 8*c + 4*jh + i
-    const uint32_t row0 = kbase + gq * 128, row1 = row0 + 8 * 128;
+    // tokens g and g + 8 share the swizzle phase; a thread reads CPT = 2 (128-byte pieces) or 1
+    // (64-byte rows) of the 16-byte chunks of each piece c of the row, chunk CPT*t + jh; word i
+    // of the cj-th chunk it reads feeds k-step 4*cj + i
+    constexpr int CPT = C::CPR / 4;
+    const uint32_t row0 = kbase + gq * C::PITCH, row1 = row0 + 8 * C::PITCH;
 #pragma unroll
-    for (int cj = 0; cj < 2 * C::NC; ++cj) {
-      const int c = cj >> 1, jh = cj & 1;
-      const uint32_t ch = (uint32_t)c * C::CHUNK_BYTES + ((uint32_t)((2 * tq + jh) ^ (gq & 7)) << 4);
+    for (int cj = 0; cj < CPT * C::NC; ++cj) {
+      const int c = cj / CPT, jh = cj % CPT;
+      const uint32_t ch = (uint32_t)c * C::CHUNK_BYTES +
+                          ((uint32_t)swizzled_chunk<C::PITCH>(CPT * tq + jh, gq) << 4);
       uint32_t w0[4], w1[4];
       lds128(row0 + ch, w0);
       lds128(row1 + ch, w1);
@@ -453,12 +468,13 @@ __device__ __forceinline__ void consume_tile(
     // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
     const int mi = lane >> 3;
     const int token = 8 * (mi >> 1) + (lane & 7);
-    const uint32_t row = vbase + token * 128;
+    const uint32_t row = vbase + token * C::PITCH;
 #pragma unroll
     for (int mt = 0; mt < C::MT; ++mt) {
-      const int chunk = ((2 * mt) & 7) + (mi & 1);
+      const int chunk = ((2 * mt) % C::CPR) + (mi & 1);
       uint32_t a[4];
-      ldmatrix_x4_trans(row + (mt >> 2) * C::CHUNK_BYTES + ((chunk ^ (token & 7)) << 4), a);
+      ldmatrix_x4_trans(row + ((2 * mt) / C::CPR) * C::CHUNK_BYTES +
+                            (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
       if constexpr (kMaskV) {
         a[0] &= keep_lo;
         a[1] &= keep_lo;
@@ -479,9 +495,9 @@ __device__ __forceinline__ void consume_tile(
       uint32_t r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int chunk = ((2 * jj) & 7) + (gq >> 2);  // within 128-byte piece jj / 4 of the row
-        r[k] = lds32(vbase + (jj >> 2) * C::CHUNK_BYTES + tk[k] * 128 + ((chunk ^ (tk[k] & 7)) << 4) +
-                     ((gq & 3) << 2));
+        const int chunk = ((2 * jj) % C::CPR) + (gq >> 2);  // within piece 2*jj / CPR of the row
+        r[k] = lds32(vbase + ((2 * jj) / C::CPR) * C::CHUNK_BYTES + tk[k] * C::PITCH +
+                     (swizzled_chunk<C::PITCH>(chunk, tk[k]) << 4) + ((gq & 3) << 2));
         if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
       }
       // bytes (c0, c2) and (c1, c3) of the token pairs side by side
@@ -851,10 +867,12 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
           c_lo = 16 * ks + 2 * tq;
           c_hi = c_lo + 8;
         } else {
-          // every 128-byte piece of an 8-bit row is read as its 16-byte chunks 2t and 2t+1;
-          // k-step ks uses word ks % 4 of chunk 2t + (ks / 4) % 2 of piece ks / 8, whose four
-          // elements fill the thread's four k slots
-          c_lo = 128 * (ks >> 3) + 32 * tq + 16 * ((ks >> 2) & 1) + 4 * (ks & 3);
+          // every piece of an 8-bit row is read as its 16-byte chunks CPT*t .. CPT*t + CPT-1
+          // (CPT = 2 for 128-byte pieces, 1 for 64-byte rows); k-step ks uses word ks % 4 of the
+          // (ks / 4)-th chunk the thread reads, whose four elements fill its four k slots
+          constexpr int CPT = C::CPR / 4;
+          const int cj = ks >> 2;
+          c_lo = C::PITCH * (cj / CPT) + 16 * (CPT * tq + cj % CPT) + 4 * (ks & 3);
           c_hi = c_lo + 2;
         }
         qb[ks][ng][0] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_lo)) : 0u;
@@ -902,7 +920,7 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
       }
       if (meta[st] == 0) {
         const uint32_t sbase = stage0 + (uint32_t)st * C::STAGE_BYTES;
-        const uint32_t kbase = sbase + role * (kTileTokens * 128);
+        const uint32_t kbase = sbase + role * (kTileTokens * C::PITCH);
         const uint32_t scales = sbase + 2 * C::TILE_BYTES + kvh * 2;
         const int remaining = vi.hi - (vi.lo + j * kTileTokens);
         if (remaining >= kTileTokens)

@@ -78,13 +78,16 @@ def test_validation_without_a_device():
     assert lib.pd_decode(None) == -1 and lib.pd_merge(None) == -1 and lib.pd_gather(None) == -1
 
 
-@pytest.mark.parametrize("kv_dtype,d,expect", [("fp16", 64, 2), ("fp16", 128, 2), ("fp16", 256, 2), ("fp16", 32, 1),
-                                               ("int8", 128, 2), ("int8", 256, 2), ("int8", 64, 1), ("int8", 32, 1),
-                                               ("fp8_e5m2", 256, 2), ("fp8_e5m2", 64, 1)])
+@pytest.mark.parametrize("kv_dtype,d,expect", [("fp16", 32, 2), ("fp16", 64, 2), ("fp16", 128, 2), ("fp16", 256, 2),
+                                               ("bf16", 32, 2), ("int8", 64, 2), ("int8", 128, 2), ("int8", 256, 2),
+                                               ("fp8_e5m2", 64, 2), ("fp8_e5m2", 256, 2),
+                                               ("int8", 32, 1), ("fp8_e5m2", 32, 1)])
 def test_kernel_selection_by_row_width(kv_dtype, d, expect):
-    """The streaming kernel (2) takes rows of one, two or four 128-byte pieces; narrower rows
-    go to the general kernel (1)."""
+    """The streaming kernel (2) takes rows of 64 bytes and of one, two or four 128-byte pieces;
+    32-byte rows go to the general kernel (1)."""
     q, cache = _cpu_case(hq=16, hkv=4, d=d, kv_dtype=kv_dtype)
+    if kv_dtype == "bf16":
+        q = q.to(torch.bfloat16)
     args = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
     assert _cabi.load().pd_select_kernel(ctypes.byref(args)) == expect
 

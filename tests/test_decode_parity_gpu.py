@@ -227,17 +227,38 @@ def test_head_dim_256_on_8bit_pages(hq, hkv, kv, scaled, kernel):
         helpers.assert_close(_run(case, kernel, splits), ref, what=f"D256 {hq}/{hkv} {kv}")
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("hq,hkv,d,kv,scaled", [
+    (14, 2, 64, "int8", True), (14, 2, 64, "fp8_e5m2", False), (16, 8, 64, "fp8_e5m2", True),
+    (24, 2, 64, "int8", True), (4, 4, 64, "int8", True),
+    (14, 2, 32, "fp16", None), (16, 8, 32, "bf16", None), (24, 2, 32, "fp16", None), (3, 1, 32, "fp16", None)])
+def test_64_byte_rows(hq, hkv, d, kv, scaled, kernel):
+    """Rows of 64 bytes (head_dim 64 on 8-bit pages, 32 on 16-bit pages) move with the 64-byte
+    swizzle: both kernels, every head-block width, one and two n-tiles, ragged lengths."""
+    io = "bf16" if kv == "bf16" else "fp16"
+    case = cases.Case("row64", hq, hkv, d, 16, kv, (150, 17, 64, 1, 1300), seed=61, scaled=scaled,
+                      scale_kind="uniform" if kv == "fp8_e5m2" else "quant", io_dtype=io)
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    if kernel == "stream":
+        cache = helpers.to_device_cache(oc)
+        q = helpers.q_to_device(case, q_np)
+        assert pdec.selected_kernel(pdec.build_args(q, cache, torch.empty_like(q))) == "stream"
+    for splits in (None, 3):
+        helpers.assert_close(_run(case, kernel, splits), ref, bf16=io == "bf16", what=f"row64 {hq}/{hkv} D{d} {kv}")
+
+
 @pytest.mark.parametrize("kv", ["int8", "fp8_e5m2"])
-def test_8bit_pages_with_narrow_rows_take_the_general_kernel(kv):
-    """head_dim 64 on 8-bit pages is a 64-byte row, which the streaming kernel does not serve:
+def test_8bit_pages_with_32_byte_rows_take_the_general_kernel(kv):
+    """head_dim 32 on 8-bit pages is a 32-byte row, which the streaming kernel does not serve:
     `auto` must pick the general kernel and still match."""
-    case = cases.Case("d64q", 14, 2, 64, 16, kv, (150, 17, 64), seed=61)
+    case = cases.Case("d32q", 14, 2, 32, 16, kv, (150, 17, 64), seed=61)
     q_np, oc = cases.build(case)
     cache = helpers.to_device_cache(oc)
     q = helpers.q_to_device(case, q_np)
     assert pdec.selected_kernel(pdec.build_args(q, cache, torch.empty_like(q))) == "simple"
     ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
-    helpers.assert_close(_run(case, "auto", None), ref, what=f"D64 {kv}")
+    helpers.assert_close(_run(case, "auto", None), ref, what=f"D32 {kv}")
 
 
 def test_merge_partials_matches_oracle():

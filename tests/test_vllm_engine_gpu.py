@@ -1,0 +1,36 @@
+"""A real vLLM engine (random weights, Qwen2.5-0.5B attention shape) served by the B200 backend.
+
+Runs ``examples/vllm_engine_check.py`` in its own process: the engine generates from the same
+seeded prompts with its stock Triton attention backend and with this library registered as the
+CUSTOM backend; the script compares log-probabilities step by step and reads the call counters
+(the check the reference's serving bench prints, ``integration/bench_vllm.py:162-170``).
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import json
+import pathlib
+import subprocess
+import sys
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+@pytest.mark.gpu
+def test_engine_decode_steps_are_served_here_and_match_the_stock_backend():
+    if importlib.util.find_spec("vllm") is None:
+        pytest.skip("vLLM is not installed")
+    run = subprocess.run([sys.executable, str(ROOT / "examples" / "vllm_engine_check.py")],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    lines = [ln for ln in run.stdout.splitlines() if ln.startswith('{"check"')]
+    assert lines, run.stdout[-2000:] + run.stderr[-4000:]
+    res = json.loads(lines[-1])
+    assert run.returncode == 0 and res["ok"], res
+    # every pure-decode step of every layer ran here; only prefill and profiling were delegated
+    assert res["stats"]["decode_calls"] == res["expected_decode_calls"]
+    assert res["stats"]["decode_tokens"] == res["expected_decode_calls"] * 24
+    assert 0 < res["stats"]["delegated_calls"] < res["stats"]["decode_calls"]
+    assert res["steps_compared"] >= 48 and res["max_abs_logprob_delta"] <= res["tol"]
