@@ -19,18 +19,32 @@ import pytest
 ROOT = pathlib.Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.gpu
-def test_engine_decode_steps_are_served_here_and_match_the_stock_backend():
+def _run_check(*flags):
     if importlib.util.find_spec("vllm") is None:
         pytest.skip("vLLM is not installed")
-    run = subprocess.run([sys.executable, str(ROOT / "examples" / "vllm_engine_check.py")],
+    run = subprocess.run([sys.executable, str(ROOT / "examples" / "vllm_engine_check.py"), *flags],
                          capture_output=True, text=True, timeout=600, cwd=ROOT)
     lines = [ln for ln in run.stdout.splitlines() if ln.startswith('{"check"')]
     assert lines, run.stdout[-2000:] + run.stderr[-4000:]
     res = json.loads(lines[-1])
     assert run.returncode == 0 and res["ok"], res
+    assert res["steps_compared"] >= 48 and res["max_abs_logprob_delta"] <= res["tol"]
+    return res
+
+
+@pytest.mark.gpu
+def test_engine_decode_steps_are_served_here_and_match_the_stock_backend():
+    res = _run_check()
     # every pure-decode step of every layer ran here; only prefill and profiling were delegated
     assert res["stats"]["decode_calls"] == res["expected_decode_calls"]
     assert res["stats"]["decode_tokens"] == res["expected_decode_calls"] * 24
     assert 0 < res["stats"]["delegated_calls"] < res["stats"]["decode_calls"]
-    assert res["steps_compared"] >= 48 and res["max_abs_logprob_delta"] <= res["tol"]
+
+
+@pytest.mark.gpu
+def test_engine_captures_the_decode_path_into_its_cuda_graphs():
+    """The engine records whole decode batches into CUDA graphs and replays them: the decode
+    call must be capturable as the engine issues it (no synchronisation, lengths read on the
+    device at replay) and the replays must give the stock backend's results."""
+    res = _run_check("--cudagraph")
+    assert res["cudagraph"] and res["stats"]["decode_calls"] > 0
