@@ -194,6 +194,9 @@ __device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t (&r)[2]) {
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t r;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
@@ -485,52 +488,61 @@ __device__ __forceinline__ void consume_tile(
       for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
     }
   } else {
-    // 8-bit V: the thread reads, from each of its four tokens, the 32-bit word of head_dim
-    // columns 32*jj + 4*g .. +3 and transposes bytes in registers.  m-tile 2*jj + h then holds
-    // column 32*jj + 4*g + 2*h in its row g and column + 1 in its row g + 8; the epilogue
-    // writes them back in order.
+    // 8-bit V: from each of its four tokens the thread reads BPT = PITCH / 8 contiguous bytes of
+    // every piece c of the row (one 16- or 8-byte load) - head_dim columns c*PITCH + BPT*g ..
+    // + BPT-1 - and transposes bytes in registers.  m-tile c*(PITCH/16) + 2*i + h then holds
+    // column c*PITCH + BPT*g + 4*i + 2*h in its row g and the next column in its row g + 8; the
+    // epilogue writes the thread's BPT columns back as one contiguous run.
+    constexpr int WPT = C::PITCH / 32;  // 32-bit words per thread, token and piece
     const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
 #pragma unroll
-    for (int jj = 0; jj < D / 32; ++jj) {
-      uint32_t r[4];
+    for (int c = 0; c < C::NC; ++c) {
+      uint32_t r[4][WPT];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int chunk = ((2 * jj) % C::CPR) + (gq >> 2);  // within piece 2*jj / CPR of the row
-        r[k] = lds32(vbase + ((2 * jj) / C::CPR) * C::CHUNK_BYTES + tk[k] * C::PITCH +
-                     (swizzled_chunk<C::PITCH>(chunk, tk[k]) << 4) + ((gq & 3) << 2));
-        if constexpr (KV == PD_KV_I8) r[k] ^= 0x80808080u;
-      }
-      // bytes (c0, c2) and (c1, c3) of the token pairs side by side
-      const uint32_t e01 = __byte_perm(r[0], r[1], 0x6240u), o01 = __byte_perm(r[0], r[1], 0x7351u);
-      const uint32_t e23 = __byte_perm(r[2], r[3], 0x6240u), o23 = __byte_perm(r[2], r[3], 0x7351u);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t a[4];
+        const uint32_t row = vbase + c * C::CHUNK_BYTES + tk[k] * C::PITCH;
+        if constexpr (C::PITCH == 128) lds128(row + (swizzled_chunk<128>(gq, tk[k]) << 4), r[k]);
+        else lds64(row + (swizzled_chunk<64>(gq >> 1, tk[k]) << 4) + ((gq & 1) << 3), r[k]);
         if constexpr (KV == PD_KV_I8) {
-          // int8 values enter as 1152 + x (one prmt each); a second mma with the constant
-          // -1152 on the same P^T takes the surplus out again inside the accumulator, tile by
-          // tile, so the sum never carries the bias
-          a[0] = cvt_pair_biased(e01, h != 0);
-          a[1] = cvt_pair_biased(o01, h != 0);
-          a[2] = cvt_pair_biased(e23, h != 0);
-          a[3] = cvt_pair_biased(o23, h != 0);
-          const uint32_t neg[4] = {0xE480E480u, 0xE480E480u, 0xE480E480u, 0xE480E480u};
 #pragma unroll
-          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], neg, pb[ng][0], pb[ng][1]);
-        } else {
-          a[0] = cvt_pair<KV>(e01, h != 0);
-          a[1] = cvt_pair<KV>(o01, h != 0);
-          a[2] = cvt_pair<KV>(e23, h != 0);
-          a[3] = cvt_pair<KV>(o23, h != 0);
+          for (int i = 0; i < WPT; ++i) r[k][i] ^= 0x80808080u;
         }
-        if constexpr (kMaskV) {
-          a[0] &= keep_lo;
-          a[1] &= keep_lo;
-          a[2] &= keep_hi;
-          a[3] &= keep_hi;
-        }
+      }
 #pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[2 * jj + h][ng], a, pb[ng][0], pb[ng][1]);
+      for (int i = 0; i < WPT; ++i) {
+        // bytes (c0, c2) and (c1, c3) of the token pairs side by side
+        const uint32_t e01 = __byte_perm(r[0][i], r[1][i], 0x6240u), o01 = __byte_perm(r[0][i], r[1][i], 0x7351u);
+        const uint32_t e23 = __byte_perm(r[2][i], r[3][i], 0x6240u), o23 = __byte_perm(r[2][i], r[3][i], 0x7351u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int mt = c * (C::PITCH / 16) + 2 * i + h;
+          uint32_t a[4];
+          if constexpr (KV == PD_KV_I8) {
+            // int8 values enter as 1152 + x (one prmt each); a second mma with the constant
+            // -1152 on the same P^T takes the surplus out again inside the accumulator, tile by
+            // tile, so the sum never carries the bias
+            a[0] = cvt_pair_biased(e01, h != 0);
+            a[1] = cvt_pair_biased(o01, h != 0);
+            a[2] = cvt_pair_biased(e23, h != 0);
+            a[3] = cvt_pair_biased(o23, h != 0);
+            const uint32_t neg[4] = {0xE480E480u, 0xE480E480u, 0xE480E480u, 0xE480E480u};
+#pragma unroll
+            for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], neg, pb[ng][0], pb[ng][1]);
+          } else {
+            a[0] = cvt_pair<KV>(e01, h != 0);
+            a[1] = cvt_pair<KV>(o01, h != 0);
+            a[2] = cvt_pair<KV>(e23, h != 0);
+            a[3] = cvt_pair<KV>(o23, h != 0);
+          }
+          if constexpr (kMaskV) {
+            a[0] &= keep_lo;
+            a[1] &= keep_lo;
+            a[2] &= keep_hi;
+            a[3] &= keep_hi;
+          }
+#pragma unroll
+          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
+        }
       }
     }
   }
@@ -978,18 +990,34 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
             }
           }
         } else {
+          // the thread's BPT = PITCH / 8 contiguous columns of every piece, eight at a time:
+          // word i of piece c came from m-tiles c*(PITCH/16) + 2*i and + 1 (rows g and g + 8)
+          constexpr int WPT = C::PITCH / 32;
 #pragma unroll
-          for (int jj = 0; jj < D / 32; ++jj) {
-            const float x0 = o[2 * jj][ng][e] * inv, x1 = o[2 * jj][ng][2 + e] * inv;
-            const float x2 = o[2 * jj + 1][ng][e] * inv, x3 = o[2 * jj + 1][ng][2 + e] * inv;
-            const int col = 32 * jj + 4 * gq;
-            if (dst16) {
-              uint2 pk;
-              pk.x = pack_io2<KV>(x0, x1);
-              pk.y = pack_io2<KV>(x2, x3);
-              *reinterpret_cast<uint2*>(dst16 + col) = pk;
+          for (int c = 0; c < C::NC; ++c) {
+#pragma unroll
+            for (int i = 0; i < WPT; i += 2) {
+              float x[8];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int mt = c * (C::PITCH / 16) + 2 * i + k;
+                x[2 * k] = o[mt][ng][e] * inv;
+                x[2 * k + 1] = o[mt][ng][2 + e] * inv;
+              }
+              const int col = c * C::PITCH + (C::PITCH / 8) * gq + 4 * i;
+              if (dst16) {
+                uint4 pk;
+                pk.x = pack_io2<KV>(x[0], x[1]);
+                pk.y = pack_io2<KV>(x[2], x[3]);
+                pk.z = pack_io2<KV>(x[4], x[5]);
+                pk.w = pack_io2<KV>(x[6], x[7]);
+                *reinterpret_cast<uint4*>(dst16 + col) = pk;
+              }
+              if (dst32) {
+                *reinterpret_cast<float4*>(dst32 + col) = make_float4(x[0], x[1], x[2], x[3]);
+                *reinterpret_cast<float4*>(dst32 + col + 4) = make_float4(x[4], x[5], x[6], x[7]);
+              }
             }
-            if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
           }
         }
       }
