@@ -16,7 +16,8 @@
 //
 // Math.  Each consumer warp keeps the (padded to 16) query rows of its group as mma A
 // fragments in registers, computes S = Q K^T with mma.sync m16n8k16 (K rows via ldmatrix, or
-// 16-byte shared loads plus in-register int8 / e5m2 -> f16 conversion), applies a base-2
+// 16-byte shared loads plus in-register e5m2 -> f16 conversion; int8 keys run unconverted on
+// the integer path, m16n8k32, against the query split into two int8 digits), applies a base-2
 // online softmax with warp shuffles (the reference's recurrence,
 // pagedattn/triton_decode.py:159-166), and accumulates O += P V in fp32.  Scales factor out of
 // both contractions: S is multiplied by the K scale per token, P by the V scale per token, so
@@ -232,6 +233,14 @@ __device__ __forceinline__ void mma_kv(float (&c)[4], const uint32_t (&a)[4], ui
   if constexpr (KV == PD_KV_BF16) mma_bf16(c, a, b0, b1);
   else mma_f16(c, a, b0, b1);
 }
+// D (16x8, s32) += A (16x32, s8, row) * B (32x8, s8, col)
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -333,7 +342,7 @@ template <int KV, int D, int HB, bool SCALED, int NG, bool MASKED>
 __device__ __forceinline__ void consume_tile(
     const uint32_t kbase, const uint32_t scales, const int hkv, const int valid,
     const float scale_log2, const int lane,
-    const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qbias)[NG][2],
+    const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qstep)[NG][2],
     float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4]) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
@@ -364,6 +373,12 @@ __device__ __forceinline__ void consume_tile(
     // of the cj-th chunk it reads feeds k-step 4*cj + i
     constexpr int CPT = C::CPR / 4;
     const uint32_t row0 = kbase + gq * C::PITCH, row1 = row0 + 8 * C::PITCH;
+    int s_hi[NG][4], s_lo[NG][4];
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s_hi[ng][r] = s_lo[ng][r] = 0;
+    }
 #pragma unroll
     for (int cj = 0; cj < CPT * C::NC; ++cj) {
       const int c = cj / CPT, jh = cj % CPT;
@@ -372,23 +387,39 @@ __device__ __forceinline__ void consume_tile(
       uint32_t w0[4], w1[4];
       lds128(row0 + ch, w0);
       lds128(row1 + ch, w1);
+      if constexpr (KV == PD_KV_I8) {
+        // int8 keys go to the integer tensor-core path as they are: words 2*m2 and 2*m2 + 1 of
+        // the chunk are the two k halves of one m16n8k32 step, against the query's high and low
+        // int8 digits (qb[.][.][0] and [1], see the prologue); no conversion instructions
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t a[4];
-        if constexpr (KV == PD_KV_I8) {
-          const uint32_t x0 = w0[i] ^ 0x80808080u, x1 = w1[i] ^ 0x80808080u;
-          a[0] = cvt_pair_biased(x0, false);
-          a[1] = cvt_pair_biased(x1, false);
-          a[2] = cvt_pair_biased(x0, true);
-          a[3] = cvt_pair_biased(x1, true);
-        } else {
+        for (int m2 = 0; m2 < 2; ++m2) {
+          const uint32_t a[4] = {w0[2 * m2], w1[2 * m2], w0[2 * m2 + 1], w1[2 * m2 + 1]};
+          const int ks = 4 * cj + 2 * m2;
+#pragma unroll
+          for (int ng = 0; ng < NG; ++ng) {
+            mma_s8(s_hi[ng], a, qb[ks][ng][0], qb[ks + 1][ng][0]);
+            mma_s8(s_lo[ng], a, qb[ks][ng][1], qb[ks + 1][ng][1]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t a[4];
           a[0] = cvt_pair<KV>(w0[i], false);
           a[1] = cvt_pair<KV>(w1[i], false);
           a[2] = cvt_pair<KV>(w0[i], true);
           a[3] = cvt_pair<KV>(w1[i], true);
-        }
 #pragma unroll
-        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
+          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
+        }
+      }
+    }
+    if constexpr (KV == PD_KV_I8) {
+      // exact integer dot products with the two digits; the query's step size comes in below
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[ng][r] = (float)(s_hi[ng][r] * 128 + s_lo[ng][r]);
       }
     }
   }
@@ -409,11 +440,11 @@ __device__ __forceinline__ void consume_tile(
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) {
     float x0 = s[ng][0], x1 = s[ng][1], x2 = s[ng][2], x3 = s[ng][3];
-    if constexpr (KV == PD_KV_I8) {
-      x0 -= qbias[ng][0];
-      x1 -= qbias[ng][1];
-      x2 -= qbias[ng][0];
-      x3 -= qbias[ng][1];
+    if constexpr (KV == PD_KV_I8) {  // the quantisation step of the query rows of heads 2t, 2t+1
+      x0 *= qstep[ng][0];
+      x1 *= qstep[ng][1];
+      x2 *= qstep[ng][0];
+      x3 *= qstep[ng][1];
     }
     x0 *= f0;
     x1 *= f0;
@@ -891,24 +922,47 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         qb[ks][ng][1] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_hi)) : 0u;
       }
     }
-    // int8 keys are fed to the tensor core as 1152 + x (cvt_pair_biased); the surplus
-    // 1152 * sum_d q[head][d] is removed from the scores of heads 2t and 2t+1 afterwards
-    float qbias[NG][2];
+    // int8 keys meet the query on the integer tensor-core path.  Each query row is written as
+    // step * (128 * hi + lo) with int8 digits hi in [-127, 127] and lo in [-64, 63], step =
+    // max|q| / 16256: 15 bits relative to the row's largest element, finer than the fp16 inputs'
+    // own spacing for all but their smallest elements.  The four elements of k-step ks are
+    // packed as the bytes of qb[ks][.][0] (hi) and qb[ks][.][1] (lo); the scores of heads 2t and
+    // 2t+1 are multiplied by those heads' steps afterwards.
+    float qstep[NG][2];
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-      qbias[ng][0] = qbias[ng][1] = 0.f;
+      qstep[ng][0] = qstep[ng][1] = 0.f;
       if constexpr (KV == PD_KV_I8) {
-        float hs = 0.f;
+        float amax = 0.f;
 #pragma unroll
         for (int ks = 0; ks < C::KSTEPS; ++ks) {
           const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][0]));
           const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][1]));
-          hs += (x.x + x.y) + (y.x + y.y);
+          amax = fmaxf(fmaxf(amax, fmaxf(fabsf(x.x), fabsf(x.y))), fmaxf(fabsf(y.x), fabsf(y.y)));
         }
-        hs += __shfl_xor_sync(kFull, hs, 1);
-        hs += __shfl_xor_sync(kFull, hs, 2);  // sum over head_dim of head g
-        qbias[ng][0] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq));
-        qbias[ng][1] = 1152.f * __shfl_sync(kFull, hs, 4 * (2 * tq + 1));
+        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));  // over head_dim of head g
+        const float inv = amax > 0.f ? 16256.f / amax : 0.f;
+        const float step = amax * (1.f / 16256.f);
+#pragma unroll
+        for (int ks = 0; ks < C::KSTEPS; ++ks) {
+          const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][0]));
+          const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&qb[ks][ng][1]));
+          const float e[4] = {x.x, x.y, y.x, y.y};
+          uint32_t hi_w = 0, lo_w = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int v = __float2int_rn(e[k] * inv);
+            const int hi = (v + 64) >> 7;
+            const int lo = v - (hi << 7);
+            hi_w |= (uint32_t)(hi & 0xff) << (8 * k);
+            lo_w |= (uint32_t)(lo & 0xff) << (8 * k);
+          }
+          qb[ks][ng][0] = hi_w;
+          qb[ks][ng][1] = lo_w;
+        }
+        qstep[ng][0] = __shfl_sync(kFull, step, 4 * (2 * tq));
+        qstep[ng][1] = __shfl_sync(kFull, step, 4 * (2 * tq + 1));
       }
     }
 
@@ -937,10 +991,10 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         const int remaining = vi.hi - (vi.lo + j * kTileTokens);
         if (remaining >= kTileTokens)
           consume_tile<KV, D, HB, SCALED, NG, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2,
-                                                     lane, qb, qbias, m, l, o);
+                                                     lane, qb, qstep, m, l, o);
         else
           consume_tile<KV, D, HB, SCALED, NG, true>(kbase, scales, p.hkv, remaining, p.scale_log2,
-                                                    lane, qb, qbias, m, l, o);
+                                                    lane, qb, qstep, m, l, o);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * st);
