@@ -353,6 +353,10 @@ __device__ __forceinline__ void consume_tile(
   float s[NG][4];
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) s[ng][0] = s[ng][1] = s[ng][2] = s[ng][3] = 0.f;
+  // even and odd k-steps accumulate separately: two dependent chains of half the length
+  float s_odd[NG][4];
+#pragma unroll
+  for (int ng = 0; ng < NG; ++ng) s_odd[ng][0] = s_odd[ng][1] = s_odd[ng][2] = s_odd[ng][3] = 0.f;
   if constexpr (is_16bit(KV)) {
     // A fragments by ldmatrix: matrices (tokens 0-7, lo), (8-15, lo), (0-7, hi), (8-15, hi) where
     // lo/hi are the two 16-byte chunks of the k-step
@@ -365,7 +369,7 @@ __device__ __forceinline__ void consume_tile(
       uint32_t a[4];
       ldmatrix_x4(row + ((2 * ks) / C::CPR) * C::CHUNK_BYTES + (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
+      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(ks & 1 ? s_odd[ng] : s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
     }
   } else {
     // tokens g and g + 8 share the swizzle phase; a thread reads CPT = 2 (128-byte pieces) or 1
@@ -373,7 +377,7 @@ __device__ __forceinline__ void consume_tile(
     // of the cj-th chunk it reads feeds k-step 4*cj + i
     constexpr int CPT = C::CPR / 4;
     const uint32_t row0 = kbase + gq * C::PITCH, row1 = row0 + 8 * C::PITCH;
-    int s_hi[NG][4], s_lo[NG][4];
+    int s_hi[NG][4], s_lo[NG][4];  // int8 only: the two digits are two independent chains already
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
 #pragma unroll
@@ -410,7 +414,8 @@ __device__ __forceinline__ void consume_tile(
           a[2] = cvt_pair<KV>(w0[i], true);
           a[3] = cvt_pair<KV>(w1[i], true);
 #pragma unroll
-          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
+          for (int ng = 0; ng < NG; ++ng)
+            mma_kv<KV>(i & 1 ? s_odd[ng] : s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
         }
       }
     }
@@ -421,6 +426,13 @@ __device__ __forceinline__ void consume_tile(
 #pragma unroll
         for (int r = 0; r < 4; ++r) s[ng][r] = (float)(s_hi[ng][r] * 128 + s_lo[ng][r]);
       }
+    }
+  }
+  if constexpr (KV != PD_KV_I8) {
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s[ng][r] += s_odd[ng][r];
     }
   }
 

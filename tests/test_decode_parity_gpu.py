@@ -248,6 +248,21 @@ def test_64_byte_rows(hq, hkv, d, kv, scaled, kernel):
         helpers.assert_close(_run(case, kernel, splits), ref, bf16=io == "bf16", what=f"row64 {hq}/{hkv} D{d} {kv}")
 
 
+@pytest.mark.parametrize("d,kv,scaled", [(64, "int8", True), (64, "fp8_e5m2", False), (128, "fp8_e5m2", True),
+                                         (128, "int8", True)])
+def test_many_requests_on_8bit_pages_with_eight_kv_heads(d, kv, scaled):
+    """Batches of 64 or more requests on 8-bit pages with eight kv heads run two workers per
+    CTA: cover that schedule at both row widths, with ragged lengths and empty requests."""
+    rng = np.random.Generator(np.random.PCG64(71))
+    lens = tuple(int(n) for n in rng.integers(0, 400, size=72))
+    case = cases.Case("w2", 32, 8, d, 16, kv, lens, seed=67, scaled=scaled,
+                      scale_kind="uniform" if kv == "fp8_e5m2" else "quant")
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    for splits in (None, 2):
+        helpers.assert_close(_run(case, "stream", splits), ref, what=f"two workers D{d} {kv}")
+
+
 @pytest.mark.parametrize("kv", ["int8", "fp8_e5m2"])
 def test_8bit_pages_with_32_byte_rows_take_the_general_kernel(kv):
     """head_dim 32 on 8-bit pages is a 32-byte row, which the streaming kernel does not serve:
