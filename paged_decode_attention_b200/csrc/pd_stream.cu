@@ -41,7 +41,6 @@ static Shape derive(const PdDecodeArgs* a) {
   const long long nv = (long long)s.nhb * a->batch * s.splits;
   s.nvseq = nv > INT32_MAX ? INT32_MAX : (int)nv;
   s.scaled = a->k_scale != nullptr;
-  if (s.hb == 8 && !is_16bit(a->kv_dtype) && nv >= 64) s.wpc = 2;
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   // a tile of K (or V) is hb heads x 16 tokens x the row, whatever pieces the row is moved in
   s.stage_bytes = 2 * s.hb * kTileTokens * a->head_dim * eb + (s.scaled ? 2048 : 0);
@@ -226,9 +225,6 @@ static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, cons
     static_assert(HB <= 4, "head_dim 256 runs at most four heads per block");
     return launch_wpc<KV, D, HB, SCALED, NG, 4 / HB>(sp, mk, mv, grid, smem, st);
   } else {
-    if constexpr (HB == 8 && !is_16bit(KV)) {
-      if (sp.wpc == 2) return launch_wpc<KV, D, HB, SCALED, NG, 2>(sp, mk, mv, grid, smem, st);
-    }
     return launch_wpc<KV, D, HB, SCALED, NG, base_workers_per_cta(HB)>(sp, mk, mv, grid, smem, st);
   }
 }

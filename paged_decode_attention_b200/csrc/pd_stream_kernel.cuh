@@ -56,11 +56,7 @@ constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxStages = 12;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
-// Workers per CTA: eight consumer warps' worth (at most four workers).  Kernels for 8-bit pages
-// with eight heads per block also exist with two workers (sixteen consumer warps): an 8-bit tile
-// carries half the bytes for the same instruction count, and the extra warps hide the
-// conversion latency.  Every worker adds a segment to each request it touches, so the host
-// picks two only for batches with many requests (see derive()).
+// Workers per CTA: eight consumer warps' worth (at most four workers).
 __host__ __device__ constexpr int base_workers_per_cta(int hb) { return 8 / hb < 4 ? 8 / hb : 4; }
 
 template <int KV, int D, int HB, bool SCALED>
@@ -337,136 +333,164 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // state (m, l) stays in the thread; P^T reaches the B-operand layout with two movmatrix.
 // `kbase` is the warp's K rows in the stage (V follows at TILE_BYTES), `scales` the address of
 // this head's K scale of token 0 (V scales 1024 bytes further, token pitch hkv * 2).
-// MASKED tiles hold fewer than 16 live tokens (`valid`); full tiles skip every mask.
-template <int KV, int D, int HB, bool SCALED, int NG, bool MASKED>
+// MASKED: the last tile holds fewer than 16 live tokens (`valid`); full tiles skip every mask.
+// NT = 2 takes two consecutive tiles of the same request (two stages) as one 32-token softmax
+// step: one running-maximum update, one rescale, and two independent score chains in flight.
+template <int KV, int D, int HB, bool SCALED, int NG, bool MASKED, int NT = 1>
 __device__ __forceinline__ void consume_tile(
-    const uint32_t kbase, const uint32_t scales, const int hkv, const int valid,
+    const uint32_t (&kbase)[NT], const uint32_t (&scales)[NT], const int hkv, const int valid,
     const float scale_log2, const int lane,
     const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qstep)[NG][2],
     float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4]) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
   const int gq = lane >> 2, tq = lane & 3;
-  const uint32_t vbase = kbase + C::TILE_BYTES;
 
   // ---- S^T = K Q^T ------------------------------------------------------------------------------
-  float s[NG][4];
+  // Two accumulators per n-tile keep two dependent chains in flight: one per tile when NT = 2,
+  // else one for the even and one for the odd k-steps (summed below).
+  float s[2][NG][4];
 #pragma unroll
-  for (int ng = 0; ng < NG; ++ng) s[ng][0] = s[ng][1] = s[ng][2] = s[ng][3] = 0.f;
-  // even and odd k-steps accumulate separately: two dependent chains of half the length
-  float s_odd[NG][4];
+  for (int u = 0; u < 2; ++u) {
 #pragma unroll
-  for (int ng = 0; ng < NG; ++ng) s_odd[ng][0] = s_odd[ng][1] = s_odd[ng][2] = s_odd[ng][3] = 0.f;
+    for (int ng = 0; ng < NG; ++ng) s[u][ng][0] = s[u][ng][1] = s[u][ng][2] = s[u][ng][3] = 0.f;
+  }
   if constexpr (is_16bit(KV)) {
     // A fragments by ldmatrix: matrices (tokens 0-7, lo), (8-15, lo), (0-7, hi), (8-15, hi) where
     // lo/hi are the two 16-byte chunks of the k-step
     const int mi = lane >> 3;
     const int token = 8 * (mi & 1) + (lane & 7);
-    const uint32_t row = kbase + token * C::PITCH;
 #pragma unroll
     for (int ks = 0; ks < C::KSTEPS; ++ks) {
       const int chunk = ((2 * ks) % C::CPR) + (mi >> 1);
-      uint32_t a[4];
-      ldmatrix_x4(row + ((2 * ks) / C::CPR) * C::CHUNK_BYTES + (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
+      const uint32_t off = token * C::PITCH + ((2 * ks) / C::CPR) * C::CHUNK_BYTES +
+                           (swizzled_chunk<C::PITCH>(chunk, token) << 4);
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(ks & 1 ? s_odd[ng] : s[ng], a, qb[ks][ng][0], qb[ks][ng][1]);
+      for (int u = 0; u < NT; ++u) {
+        uint32_t a[4];
+        ldmatrix_x4(kbase[u] + off, a);
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng)
+          mma_kv<KV>(s[NT == 2 ? u : (ks & 1)][ng], a, qb[ks][ng][0], qb[ks][ng][1]);
+      }
     }
   } else {
     // tokens g and g + 8 share the swizzle phase; a thread reads CPT = 2 (128-byte pieces) or 1
     // (64-byte rows) of the 16-byte chunks of each piece c of the row, chunk CPT*t + jh; word i
     // of the cj-th chunk it reads feeds k-step 4*cj + i
     constexpr int CPT = C::CPR / 4;
-    const uint32_t row0 = kbase + gq * C::PITCH, row1 = row0 + 8 * C::PITCH;
-    int s_hi[NG][4], s_lo[NG][4];  // int8 only: the two digits are two independent chains already
+    int s_hi[NT][NG][4], s_lo[NT][NG][4];  // int8 only: the two digits are independent chains
 #pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
+    for (int u = 0; u < NT; ++u) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) s_hi[ng][r] = s_lo[ng][r] = 0;
+      for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s_hi[u][ng][r] = s_lo[u][ng][r] = 0;
+      }
     }
 #pragma unroll
     for (int cj = 0; cj < CPT * C::NC; ++cj) {
       const int c = cj / CPT, jh = cj % CPT;
-      const uint32_t ch = (uint32_t)c * C::CHUNK_BYTES +
+      const uint32_t ch = gq * C::PITCH + (uint32_t)c * C::CHUNK_BYTES +
                           ((uint32_t)swizzled_chunk<C::PITCH>(CPT * tq + jh, gq) << 4);
-      uint32_t w0[4], w1[4];
-      lds128(row0 + ch, w0);
-      lds128(row1 + ch, w1);
-      if constexpr (KV == PD_KV_I8) {
-        // int8 keys go to the integer tensor-core path as they are: words 2*m2 and 2*m2 + 1 of
-        // the chunk are the two k halves of one m16n8k32 step, against the query's high and low
-        // int8 digits (qb[.][.][0] and [1], see the prologue); no conversion instructions
 #pragma unroll
-        for (int m2 = 0; m2 < 2; ++m2) {
-          const uint32_t a[4] = {w0[2 * m2], w1[2 * m2], w0[2 * m2 + 1], w1[2 * m2 + 1]};
-          const int ks = 4 * cj + 2 * m2;
+      for (int u = 0; u < NT; ++u) {
+        uint32_t w0[4], w1[4];
+        lds128(kbase[u] + ch, w0);
+        lds128(kbase[u] + ch + 8 * C::PITCH, w1);
+        if constexpr (KV == PD_KV_I8) {
+          // int8 keys go to the integer tensor-core path as they are: words 2*m2 and 2*m2 + 1
+          // of the chunk are the two k halves of one m16n8k32 step, against the query's high
+          // and low int8 digits (qb[.][.][0] and [1], see the prologue); no conversions
 #pragma unroll
-          for (int ng = 0; ng < NG; ++ng) {
-            mma_s8(s_hi[ng], a, qb[ks][ng][0], qb[ks + 1][ng][0]);
-            mma_s8(s_lo[ng], a, qb[ks][ng][1], qb[ks + 1][ng][1]);
+          for (int m2 = 0; m2 < 2; ++m2) {
+            const uint32_t a[4] = {w0[2 * m2], w1[2 * m2], w0[2 * m2 + 1], w1[2 * m2 + 1]};
+            const int ks = 4 * cj + 2 * m2;
+#pragma unroll
+            for (int ng = 0; ng < NG; ++ng) {
+              mma_s8(s_hi[u][ng], a, qb[ks][ng][0], qb[ks + 1][ng][0]);
+              mma_s8(s_lo[u][ng], a, qb[ks][ng][1], qb[ks + 1][ng][1]);
+            }
           }
-        }
-      } else {
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t a[4];
-          a[0] = cvt_pair<KV>(w0[i], false);
-          a[1] = cvt_pair<KV>(w1[i], false);
-          a[2] = cvt_pair<KV>(w0[i], true);
-          a[3] = cvt_pair<KV>(w1[i], true);
+          for (int i = 0; i < 4; ++i) {
+            uint32_t a[4];
+            a[0] = cvt_pair<KV>(w0[i], false);
+            a[1] = cvt_pair<KV>(w1[i], false);
+            a[2] = cvt_pair<KV>(w0[i], true);
+            a[3] = cvt_pair<KV>(w1[i], true);
 #pragma unroll
-          for (int ng = 0; ng < NG; ++ng)
-            mma_kv<KV>(i & 1 ? s_odd[ng] : s[ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
+            for (int ng = 0; ng < NG; ++ng)
+              mma_kv<KV>(s[NT == 2 ? u : (i & 1)][ng], a, qb[4 * cj + i][ng][0], qb[4 * cj + i][ng][1]);
+          }
         }
       }
     }
     if constexpr (KV == PD_KV_I8) {
       // exact integer dot products with the two digits; the query's step size comes in below
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) {
+      for (int u = 0; u < NT; ++u) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) s[ng][r] = (float)(s_hi[ng][r] * 128 + s_lo[ng][r]);
+        for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) s[u][ng][r] = (float)(s_hi[u][ng][r] * 128 + s_lo[u][ng][r]);
+        }
       }
     }
   }
-  if constexpr (KV != PD_KV_I8) {
+  if constexpr (NT == 1 && KV != PD_KV_I8) {
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) s[ng][r] += s_odd[ng][r];
+      for (int r = 0; r < 4; ++r) s[0][ng][r] += s[1][ng][r];
     }
   }
 
   // ---- scale, mask, online softmax; P^T into B-operand layout ---------------------------------
-  float f0 = scale_log2, f1 = scale_log2;  // tokens g and g + 8
-  float vs0 = 1.f, vs1 = 1.f;              // their V scales (times 256)
-  if constexpr (SCALED) {
-    const uint32_t sa = scales + gq * hkv * 2;
-    f0 *= lds_half(sa);
-    f1 *= lds_half(sa + 8 * hkv * 2);
-    vs0 = lds_half(sa + 1024) * 256.f;
-    vs1 = lds_half(sa + 1024 + 8 * hkv * 2) * 256.f;
+  float f[NT][2], vs[NT][2];  // score factors and V scales (times 256) of tokens g and g + 8
+#pragma unroll
+  for (int u = 0; u < NT; ++u) {
+    f[u][0] = f[u][1] = scale_log2;
+    vs[u][0] = vs[u][1] = 1.f;
+    if constexpr (SCALED) {
+      const uint32_t sa = scales[u] + gq * hkv * 2;
+      f[u][0] *= lds_half(sa);
+      f[u][1] *= lds_half(sa + 8 * hkv * 2);
+      vs[u][0] = lds_half(sa + 1024) * 256.f;
+      vs[u][1] = lds_half(sa + 1024 + 8 * hkv * 2) * 256.f;
+    }
   }
-  uint32_t pb[NG][2];
+  uint32_t pb[NT][NG][2];
   float alpha[NG][2];
   bool moved = false;
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) {
-    float x0 = s[ng][0], x1 = s[ng][1], x2 = s[ng][2], x3 = s[ng][3];
-    if constexpr (KV == PD_KV_I8) {  // the quantisation step of the query rows of heads 2t, 2t+1
-      x0 *= qstep[ng][0];
-      x1 *= qstep[ng][1];
-      x2 *= qstep[ng][0];
-      x3 *= qstep[ng][1];
+    float x[NT][4];
+    float mx0 = -INFINITY, mx1 = -INFINITY;  // heads 2t, 2t+1 over the thread's tokens
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) x[u][r] = s[u][ng][r];
+      if constexpr (KV == PD_KV_I8) {  // the quantisation step of the query rows of heads 2t, 2t+1
+        x[u][0] *= qstep[ng][0];
+        x[u][1] *= qstep[ng][1];
+        x[u][2] *= qstep[ng][0];
+        x[u][3] *= qstep[ng][1];
+      }
+      x[u][0] *= f[u][0];
+      x[u][1] *= f[u][0];
+      x[u][2] *= f[u][1];
+      x[u][3] *= f[u][1];
+      if constexpr (MASKED) {
+        if (u == NT - 1) {
+          if (gq >= valid) x[u][0] = x[u][1] = -INFINITY;
+          if (gq + 8 >= valid) x[u][2] = x[u][3] = -INFINITY;
+        }
+      }
+      mx0 = fmaxf(mx0, fmaxf(x[u][0], x[u][2]));
+      mx1 = fmaxf(mx1, fmaxf(x[u][1], x[u][3]));
     }
-    x0 *= f0;
-    x1 *= f0;
-    x2 *= f1;
-    x3 *= f1;
-    if constexpr (MASKED) {
-      if (gq >= valid) x0 = x1 = -INFINITY;
-      if (gq + 8 >= valid) x2 = x3 = -INFINITY;
-    }
-    float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);  // heads 2t, 2t+1 over the thread's tokens
 #pragma unroll
     for (int sh = 4; sh < 32; sh <<= 1) {
       mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, sh));
@@ -478,13 +502,19 @@ __device__ __forceinline__ void consume_tile(
     moved = moved || alpha[ng][0] != 1.f || alpha[ng][1] != 1.f;
     m[ng][0] = mn0;
     m[ng][1] = mn1;
-    const float p0 = fast_exp2(x0 - mn0), p1 = fast_exp2(x1 - mn1);
-    const float p2 = fast_exp2(x2 - mn0), p3 = fast_exp2(x3 - mn1);
-    l[ng][0] = l[ng][0] * alpha[ng][0] + (p0 + p2);
-    l[ng][1] = l[ng][1] * alpha[ng][1] + (p1 + p3);
-    // (token g | g+8, heads 2t, 2t+1) -> (tokens 2t, 2t+1 | 2t+8, 2t+9, head g)
-    pb[ng][0] = movmatrix_trans(SCALED ? pack_io2<KV>(p0 * vs0, p1 * vs0) : pack_io2<KV>(p0, p1));
-    pb[ng][1] = movmatrix_trans(SCALED ? pack_io2<KV>(p2 * vs1, p3 * vs1) : pack_io2<KV>(p2, p3));
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+      const float p0 = fast_exp2(x[u][0] - mn0), p1 = fast_exp2(x[u][1] - mn1);
+      const float p2 = fast_exp2(x[u][2] - mn0), p3 = fast_exp2(x[u][3] - mn1);
+      sum0 += p0 + p2;
+      sum1 += p1 + p3;
+      // (token g | g+8, heads 2t, 2t+1) -> (tokens 2t, 2t+1 | 2t+8, 2t+9, head g)
+      pb[u][ng][0] = movmatrix_trans(SCALED ? pack_io2<KV>(p0 * vs[u][0], p1 * vs[u][0]) : pack_io2<KV>(p0, p1));
+      pb[u][ng][1] = movmatrix_trans(SCALED ? pack_io2<KV>(p2 * vs[u][1], p3 * vs[u][1]) : pack_io2<KV>(p2, p3));
+    }
+    l[ng][0] = l[ng][0] * alpha[ng][0] + sum0;
+    l[ng][1] = l[ng][1] * alpha[ng][1] + sum1;
   }
   // the running maxima settle after the first tiles; skip the rescale when nobody's moved
   if (__any_sync(kFull, moved)) {
@@ -509,83 +539,105 @@ __device__ __forceinline__ void consume_tile(
     keep_lo = (2 * tq < valid ? 0x0000ffffu : 0u) | (2 * tq + 1 < valid ? 0xffff0000u : 0u);
     keep_hi = (2 * tq + 8 < valid ? 0x0000ffffu : 0u) | (2 * tq + 9 < valid ? 0xffff0000u : 0u);
   }
-  if constexpr (is_16bit(KV)) {
-    // transposed 8x8 matrices (tokens 0-7, lo), (0-7, hi), (8-15, lo), (8-15, hi) of the 16
-    // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
-    const int mi = lane >> 3;
-    const int token = 8 * (mi >> 1) + (lane & 7);
-    const uint32_t row = vbase + token * C::PITCH;
+#pragma unroll
+  for (int u = 0; u < NT; ++u) {
+    const uint32_t vbase = kbase[u] + C::TILE_BYTES;
+    const bool mask_this = kMaskV && u == NT - 1;
+    if constexpr (is_16bit(KV)) {
+      // transposed 8x8 matrices (tokens 0-7, lo), (0-7, hi), (8-15, lo), (8-15, hi) of the 16
+      // head_dim columns of m-tile mt: A rows are head_dim 16*mt + g and + 8
+      const int mi = lane >> 3;
+      const int token = 8 * (mi >> 1) + (lane & 7);
+      const uint32_t row = vbase + token * C::PITCH;
+#pragma unroll
+      for (int mt = 0; mt < C::MT; ++mt) {
+        const int chunk = ((2 * mt) % C::CPR) + (mi & 1);
+        uint32_t a[4];
+        ldmatrix_x4_trans(row + ((2 * mt) / C::CPR) * C::CHUNK_BYTES +
+                              (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
+        if (mask_this) {
+          a[0] &= keep_lo;
+          a[1] &= keep_lo;
+          a[2] &= keep_hi;
+          a[3] &= keep_hi;
+        }
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[u][ng][0], pb[u][ng][1]);
+      }
+    } else {
+      // 8-bit V: from each of its four tokens the thread reads BPT = PITCH / 8 contiguous bytes
+      // of every piece c of the row (one 16- or 8-byte load) - head_dim columns c*PITCH + BPT*g
+      // .. + BPT-1 - and transposes bytes in registers.  m-tile c*(PITCH/16) + 2*i + h then
+      // holds column c*PITCH + BPT*g + 4*i + 2*h in its row g and the next column in its row
+      // g + 8; the epilogue writes the thread's BPT columns back as one contiguous run.
+      constexpr int WPT = C::PITCH / 32;  // 32-bit words per thread, token and piece
+      const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
+#pragma unroll
+      for (int c = 0; c < C::NC; ++c) {
+        uint32_t r[4][WPT];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t row = vbase + c * C::CHUNK_BYTES + tk[k] * C::PITCH;
+          if constexpr (C::PITCH == 128) lds128(row + (swizzled_chunk<128>(gq, tk[k]) << 4), r[k]);
+          else lds64(row + (swizzled_chunk<64>(gq >> 1, tk[k]) << 4) + ((gq & 1) << 3), r[k]);
+          if constexpr (KV == PD_KV_I8) {
+#pragma unroll
+            for (int i = 0; i < WPT; ++i) r[k][i] ^= 0x80808080u;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < WPT; ++i) {
+          // bytes (c0, c2) and (c1, c3) of the token pairs side by side
+          const uint32_t e01 = __byte_perm(r[0][i], r[1][i], 0x6240u), o01 = __byte_perm(r[0][i], r[1][i], 0x7351u);
+          const uint32_t e23 = __byte_perm(r[2][i], r[3][i], 0x6240u), o23 = __byte_perm(r[2][i], r[3][i], 0x7351u);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int mt = c * (C::PITCH / 16) + 2 * i + h;
+            uint32_t a[4];
+            if constexpr (KV == PD_KV_I8) {
+              // int8 values enter as 1152 + x (one prmt each); the surplus is taken out below
+              a[0] = cvt_pair_biased(e01, h != 0);
+              a[1] = cvt_pair_biased(o01, h != 0);
+              a[2] = cvt_pair_biased(e23, h != 0);
+              a[3] = cvt_pair_biased(o23, h != 0);
+            } else {
+              a[0] = cvt_pair<KV>(e01, h != 0);
+              a[1] = cvt_pair<KV>(o01, h != 0);
+              a[2] = cvt_pair<KV>(e23, h != 0);
+              a[3] = cvt_pair<KV>(o23, h != 0);
+            }
+            if (mask_this) {
+              a[0] &= keep_lo;
+              a[1] &= keep_lo;
+              a[2] &= keep_hi;
+              a[3] &= keep_hi;
+            }
+#pragma unroll
+            for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[u][ng][0], pb[u][ng][1]);
+          }
+        }
+      }
+    }
+  }
+  if constexpr (KV == PD_KV_I8) {
+    // Every int8 value entered as 1152 + x.  One more mma with an all-ones A gives, in every row,
+    // the sum over this call's tokens of P^T exactly as the tensor core read it; 1152 times that
+    // leaves each accumulator again before the call returns, so the running sums never carry
+    // the surplus from one call to the next.
+    float cs[NG][4];
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) {
+      cs[ng][0] = cs[ng][1] = cs[ng][2] = cs[ng][3] = 0.f;
+#pragma unroll
+      for (int u = 0; u < NT; ++u) mma_kv<KV>(cs[ng], ones, pb[u][ng][0], pb[u][ng][1]);
+    }
 #pragma unroll
     for (int mt = 0; mt < C::MT; ++mt) {
-      const int chunk = ((2 * mt) % C::CPR) + (mi & 1);
-      uint32_t a[4];
-      ldmatrix_x4_trans(row + ((2 * mt) / C::CPR) * C::CHUNK_BYTES +
-                            (swizzled_chunk<C::PITCH>(chunk, token) << 4), a);
-      if constexpr (kMaskV) {
-        a[0] &= keep_lo;
-        a[1] &= keep_lo;
-        a[2] &= keep_hi;
-        a[3] &= keep_hi;
-      }
 #pragma unroll
-      for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
-    }
-  } else {
-    // 8-bit V: from each of its four tokens the thread reads BPT = PITCH / 8 contiguous bytes of
-    // every piece c of the row (one 16- or 8-byte load) - head_dim columns c*PITCH + BPT*g ..
-    // + BPT-1 - and transposes bytes in registers.  m-tile c*(PITCH/16) + 2*i + h then holds
-    // column c*PITCH + BPT*g + 4*i + 2*h in its row g and the next column in its row g + 8; the
-    // epilogue writes the thread's BPT columns back as one contiguous run.
-    constexpr int WPT = C::PITCH / 32;  // 32-bit words per thread, token and piece
-    const int tk[4] = {2 * tq, 2 * tq + 1, 2 * tq + 8, 2 * tq + 9};
+      for (int ng = 0; ng < NG; ++ng) {
 #pragma unroll
-    for (int c = 0; c < C::NC; ++c) {
-      uint32_t r[4][WPT];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t row = vbase + c * C::CHUNK_BYTES + tk[k] * C::PITCH;
-        if constexpr (C::PITCH == 128) lds128(row + (swizzled_chunk<128>(gq, tk[k]) << 4), r[k]);
-        else lds64(row + (swizzled_chunk<64>(gq >> 1, tk[k]) << 4) + ((gq & 1) << 3), r[k]);
-        if constexpr (KV == PD_KV_I8) {
-#pragma unroll
-          for (int i = 0; i < WPT; ++i) r[k][i] ^= 0x80808080u;
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < WPT; ++i) {
-        // bytes (c0, c2) and (c1, c3) of the token pairs side by side
-        const uint32_t e01 = __byte_perm(r[0][i], r[1][i], 0x6240u), o01 = __byte_perm(r[0][i], r[1][i], 0x7351u);
-        const uint32_t e23 = __byte_perm(r[2][i], r[3][i], 0x6240u), o23 = __byte_perm(r[2][i], r[3][i], 0x7351u);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int mt = c * (C::PITCH / 16) + 2 * i + h;
-          uint32_t a[4];
-          if constexpr (KV == PD_KV_I8) {
-            // int8 values enter as 1152 + x (one prmt each); a second mma with the constant
-            // -1152 on the same P^T takes the surplus out again inside the accumulator, tile by
-            // tile, so the sum never carries the bias
-            a[0] = cvt_pair_biased(e01, h != 0);
-            a[1] = cvt_pair_biased(o01, h != 0);
-            a[2] = cvt_pair_biased(e23, h != 0);
-            a[3] = cvt_pair_biased(o23, h != 0);
-            const uint32_t neg[4] = {0xE480E480u, 0xE480E480u, 0xE480E480u, 0xE480E480u};
-#pragma unroll
-            for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], neg, pb[ng][0], pb[ng][1]);
-          } else {
-            a[0] = cvt_pair<KV>(e01, h != 0);
-            a[1] = cvt_pair<KV>(o01, h != 0);
-            a[2] = cvt_pair<KV>(e23, h != 0);
-            a[3] = cvt_pair<KV>(o23, h != 0);
-          }
-          if constexpr (kMaskV) {
-            a[0] &= keep_lo;
-            a[1] &= keep_lo;
-            a[2] &= keep_hi;
-            a[3] &= keep_hi;
-          }
-#pragma unroll
-          for (int ng = 0; ng < NG; ++ng) mma_kv<KV>(o[mt][ng], a, pb[ng][0], pb[ng][1]);
-        }
+        for (int r = 0; r < 4; ++r) o[mt][ng][r] = fmaf(-1152.f, cs[ng][r], o[mt][ng][r]);
       }
     }
   }
@@ -990,26 +1042,66 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
 #pragma unroll
       for (int ng = 0; ng < NG; ++ng) o[mt][ng][0] = o[mt][ng][1] = o[mt][ng][2] = o[mt][ng][3] = 0.f;
 
-    for (; g < seg_end; ++g, ++j, ++it) {
+    // 8-bit tiles with a deep ring (five stages or more) are taken two at a time: one softmax
+    // step per 32 tokens and two independent score chains per warp.  With fewer stages the
+    // second stage held by the consumers would cost the producer its lead.
+    constexpr bool kPairs = !is_16bit(KV);
+    const bool pairs = kPairs && nstage >= 5;
+    while (g < seg_end) {
       const int st = it % nstage;
       if (!mbar_wait(full0 + 8 * st, (uint32_t)(it / nstage) & 1u, p.status, abort_flag)) {
         aborted = true;
         break;
       }
+      const uint32_t sbase = stage0 + (uint32_t)st * C::STAGE_BYTES;
+      const int remaining = vi.hi - (vi.lo + j * kTileTokens);
+      if constexpr (kPairs) {
+        if (pairs && g + 1 < seg_end) {
+          const int st1 = (it + 1) % nstage;
+          if (!mbar_wait(full0 + 8 * st1, (uint32_t)((it + 1) / nstage) & 1u, p.status, abort_flag)) {
+            aborted = true;
+            break;
+          }
+          if (meta[st] == 0 && meta[st1] == 0) {
+            const uint32_t sbase1 = stage0 + (uint32_t)st1 * C::STAGE_BYTES;
+            const uint32_t kb[2] = {sbase + role * (kTileTokens * C::PITCH),
+                                    sbase1 + role * (kTileTokens * C::PITCH)};
+            const uint32_t sc[2] = {sbase + 2 * C::TILE_BYTES + kvh * 2, sbase1 + 2 * C::TILE_BYTES + kvh * 2};
+            const int remaining1 = remaining - kTileTokens;  // >= 1: the next tile is of this request
+            if (remaining1 >= kTileTokens)
+              consume_tile<KV, D, HB, SCALED, NG, false, 2>(kb, sc, p.hkv, kTileTokens, p.scale_log2,
+                                                            lane, qb, qstep, m, l, o);
+            else
+              consume_tile<KV, D, HB, SCALED, NG, true, 2>(kb, sc, p.hkv, remaining1, p.scale_log2,
+                                                           lane, qb, qstep, m, l, o);
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(empty0 + 8 * st);
+              mbar_arrive(empty0 + 8 * st1);
+            }
+            g += 2;
+            j += 2;
+            it += 2;
+            continue;
+          }
+          // a tile with a bad block id: take the two one by one (the second wait returns at once)
+        }
+      }
       if (meta[st] == 0) {
-        const uint32_t sbase = stage0 + (uint32_t)st * C::STAGE_BYTES;
-        const uint32_t kbase = sbase + role * (kTileTokens * C::PITCH);
-        const uint32_t scales = sbase + 2 * C::TILE_BYTES + kvh * 2;
-        const int remaining = vi.hi - (vi.lo + j * kTileTokens);
+        const uint32_t kb[1] = {sbase + role * (kTileTokens * C::PITCH)};
+        const uint32_t sc[1] = {sbase + 2 * C::TILE_BYTES + kvh * 2};
         if (remaining >= kTileTokens)
-          consume_tile<KV, D, HB, SCALED, NG, false>(kbase, scales, p.hkv, kTileTokens, p.scale_log2,
+          consume_tile<KV, D, HB, SCALED, NG, false>(kb, sc, p.hkv, kTileTokens, p.scale_log2,
                                                      lane, qb, qstep, m, l, o);
         else
-          consume_tile<KV, D, HB, SCALED, NG, true>(kbase, scales, p.hkv, remaining, p.scale_log2,
+          consume_tile<KV, D, HB, SCALED, NG, true>(kb, sc, p.hkv, remaining, p.scale_log2,
                                                     lane, qb, qstep, m, l, o);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * st);
+      ++g;
+      ++j;
+      ++it;
     }
     if (aborted) break;
 

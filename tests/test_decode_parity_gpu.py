@@ -251,8 +251,8 @@ def test_64_byte_rows(hq, hkv, d, kv, scaled, kernel):
 @pytest.mark.parametrize("d,kv,scaled", [(64, "int8", True), (64, "fp8_e5m2", False), (128, "fp8_e5m2", True),
                                          (128, "int8", True)])
 def test_many_requests_on_8bit_pages_with_eight_kv_heads(d, kv, scaled):
-    """Batches of 64 or more requests on 8-bit pages with eight kv heads run two workers per
-    CTA: cover that schedule at both row widths, with ragged lengths and empty requests."""
+    """Many short ragged requests (some empty) on 8-bit pages with eight kv heads, at both row
+    widths: segments of one, two and odd numbers of tiles through the paired-tile loop."""
     rng = np.random.Generator(np.random.PCG64(71))
     lens = tuple(int(n) for n in rng.integers(0, 400, size=72))
     case = cases.Case("w2", 32, 8, d, 16, kv, lens, seed=67, scaled=scaled,
@@ -260,7 +260,7 @@ def test_many_requests_on_8bit_pages_with_eight_kv_heads(d, kv, scaled):
     q_np, oc = cases.build(case)
     ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
     for splits in (None, 2):
-        helpers.assert_close(_run(case, "stream", splits), ref, what=f"two workers D{d} {kv}")
+        helpers.assert_close(_run(case, "stream", splits), ref, what=f"many requests D{d} {kv}")
 
 
 @pytest.mark.parametrize("kv", ["int8", "fp8_e5m2"])
