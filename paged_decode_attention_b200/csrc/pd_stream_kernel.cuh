@@ -21,7 +21,8 @@
 // online softmax with warp shuffles (the reference's recurrence,
 // pagedattn/triton_decode.py:159-166), and accumulates O += P V in fp32.  Scales factor out of
 // both contractions: S is multiplied by the K scale per token, P by the V scale per token, so
-// 8-bit pages are only ever converted, never multiplied element-wise.
+// 8-bit pages are only ever converted, never multiplied element-wise.  Where the ring holds five
+// stages or more (8-bit shapes) a warp takes two tiles per softmax step.
 //
 // Results.  A (worker, virtual sequence) segment that covers a whole unsplit request writes
 // its output row directly; any other segment writes a normalised fp32 partial plus its base-2
