@@ -6,8 +6,12 @@ counters to prove it).  This script makes the same check for the B200 backend wi
 weights on disk: it writes a small Qwen2-style ``config.json`` with the attention shape of
 Qwen2.5-0.5B (14 query heads, 2 KV heads, head_dim 64), lets the engine build the model with
 random weights (re-drawn here from a seeded generator so that attention is not degenerate),
-and generates greedily from seeded token prompts twice — once with the engine's own Triton
-attention backend, once with ``attention_backend="CUSTOM"`` after ``install()``.
+and generates greedily from seeded token prompts twice — once with the engine's own attention
+backend, once with ``attention_backend="CUSTOM"`` after ``install()``.  ``--parent`` picks the
+engine backend that the non-decode calls are delegated to (and that the stock run uses):
+``triton`` as in the reference, or ``flash`` — the reference's own next step
+(README.md:211-214), which keeps the decode path here and runs prefill on the engine's
+FlashAttention kernel.
 
 It checks that (1) the decode counter shows layers x decode-steps calls served here and only
 prefill/profiling calls delegated, and (2) at every generation step where both runs are still on
@@ -24,6 +28,7 @@ import gc
 import json
 import os
 import pathlib
+import statistics
 import sys
 import tempfile
 
@@ -101,6 +106,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=24)
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--tol", type=float, default=3e-2, help="max |delta log-prob| on shared tokens")
+    ap.add_argument("--parent", choices=("triton", "flash"), default="triton",
+                    help="engine backend the non-decode calls are delegated to")
     ap.add_argument("--cudagraph", action="store_true",
                     help="let the engine capture decode batches into CUDA graphs: the counters then "
                          "count captures and warm-ups, not replays")
@@ -111,12 +118,29 @@ def main() -> int:
     prompts = _prompts(args.batch, 64, 160, CONFIG["vocab_size"])
     with tempfile.TemporaryDirectory() as d:
         (pathlib.Path(d) / "config.json").write_text(json.dumps(CONFIG))
-        stock = _generate(d, "TRITON_ATTN", prompts, args.steps, args.cudagraph)
-        vllm_backend.install()
+        stock = _generate(d, "FLASH_ATTN" if args.parent == "flash" else "TRITON_ATTN", prompts, args.steps,
+                          args.cudagraph)
+        vllm_backend.install(parent=args.parent)
         for k in vllm_backend.STATS:
             vllm_backend.STATS[k] = 0
+        vllm_backend.TIMING.update(enabled=True, delegated_events=[], decode_host_s=[])
         ours = _generate(d, "CUSTOM", prompts, args.steps, args.cudagraph)
     stats = dict(vllm_backend.STATS)
+    import torch
+
+    torch.cuda.synchronize()
+    # delegated calls that carried tokens are the prefill attention of each layer
+    prefill = [(e0.elapsed_time(e1), n) for e0, e1, n in vllm_backend.TIMING["delegated_events"] if n > 0]
+    timing = {"parent": args.parent,
+              "delegated_attention_ms_total": sum(ms for ms, _ in prefill),
+              "delegated_attention_calls": len(prefill),
+              "delegated_attention_tokens": sum(n for _, n in prefill),
+              "decode_host_us_median": 1e6 * statistics.median(vllm_backend.TIMING["decode_host_s"] or [0.0]),
+              "decode_host_us_first_calls_max": 1e6 * max(vllm_backend.TIMING["decode_host_s"] or [0.0]),
+              "note": "device time of the parent's forward on prefill and mixed batches (CUDA events); host "
+                      "wall time of one decode call of this library as the engine issues it (no device wait): "
+                      "the median is the steady state, the maximum is a first call that prepares the "
+                      "argument block and its scratch"}
 
     compared = same_tokens = total = 0
     worst = 0.0
@@ -142,7 +166,7 @@ def main() -> int:
     print(json.dumps({"check": "vllm_engine", "ok": bool(ok), "cudagraph": args.cudagraph, "stats": stats,
                       "expected_decode_calls": expect_decode, "steps_compared": compared,
                       "steps_total": total, "same_greedy_token": same_tokens,
-                      "max_abs_logprob_delta": worst, "tol": args.tol,
+                      "max_abs_logprob_delta": worst, "tol": args.tol, "timing": timing,
                       "model": "Qwen2-style random weights, 14/2 heads, head_dim 64, 4 layers"}))
     return 0 if ok else 1
 

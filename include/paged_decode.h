@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define PD_ABI_VERSION 1
+#define PD_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define PD_API __attribute__((visibility("default")))
@@ -59,6 +59,14 @@ extern "C" {
 #define PD_KERNEL_AUTO 0      /* streaming kernel when it serves the request, else the simple one */
 #define PD_KERNEL_SIMPLE 1    /* one CTA per (request, kv head, split); CUDA cores; any stride     */
 #define PD_KERNEL_STREAM 2    /* persistent TMA + mbarrier pipeline with tensor-core tiles         */
+
+/* bits of PdDecodeArgs.flags */
+#define PD_FLAG_COUNTERS_ZERO 1u /* the caller vouches that the first pd_counter_bytes() bytes of
+                                    `workspace` are zero: it zero-filled the workspace once and has
+                                    since used it only for calls with these same sizes, dtypes and
+                                    split count that completed without PD_DEV_TIMEOUT (every call
+                                    leaves its counters at zero).  The per-call clear of the
+                                    counters, one memset node ahead of the kernel, is then skipped. */
 
 /* bits of the optional device status word (PdDecodeArgs.status) */
 #define PD_DEV_BAD_BLOCK 1u   /* a block-table entry was outside [0, num_blocks): page skipped */
@@ -119,6 +127,7 @@ typedef struct PdDecodeArgs {
 
   uint32_t* status; /* optional device word, OR-ed with PD_DEV_* bits; caller zeroes it */
   void* stream;
+  uint32_t flags;   /* PD_FLAG_* bits, 0 for none */
 } PdDecodeArgs;
 
 /* Host buffers for pd_decode_host. */
@@ -200,6 +209,11 @@ PD_API int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
  * (_Workspace, pagedattn/triton_decode.py:266-282) with caller-owned memory. */
 PD_API int pd_workspace_bytes(const PdDecodeArgs* args, uint64_t* bytes);
 
+/* Bytes at the start of the workspace that hold the arrival counters of the streaming kernel's
+ * in-kernel merge (0 when the simple kernel would run): what PD_FLAG_COUNTERS_ZERO speaks of.
+ * No counterpart in the reference. */
+PD_API int pd_counter_bytes(const PdDecodeArgs* args, uint64_t* bytes);
+
 /* Which kernel pd_decode would run: PD_KERNEL_SIMPLE or PD_KERNEL_STREAM, or a negative
  * PD_ERR_* if the arguments are rejected.  Touches no device. */
 PD_API int pd_select_kernel(const PdDecodeArgs* args);
@@ -219,7 +233,9 @@ PD_API int pd_gather(const PdGatherArgs* args);
  * corresponds to it (the reference is single-GPU); the merge arithmetic is that of
  * _split_reduce_kernel (pagedattn/triton_decode.py:221-240) over ranks.  Every rank owns one
  * exchange buffer of pd_exchange_bytes() bytes, zero-filled once, mapped into every peer
- * (e.g. torch symmetric memory); `peer_bufs[r]` is rank r's buffer as seen from this rank. */
+ * (e.g. torch symmetric memory); `peer_bufs[r]` is rank r's buffer as seen from this rank.
+ * A partial arrives in pieces of `rows_per_flag` consecutive rows, each announced by its own
+ * flag, so a merge can start on the rows that are there. */
 typedef struct PdExchangeArgs {
   void* const* peer_bufs;  /* host array [world]; entry [rank] is this rank's own buffer */
   int32_t world, rank;     /* world <= 16 */
@@ -232,18 +248,46 @@ typedef struct PdExchangeArgs {
   int32_t io_dtype;
   float* result_f32;       /* optional merged fp32 result [rows, head_dim] */
   float* result_lse;       /* optional merged lse [rows] */
-  uint32_t* status;        /* optional device word: PD_DEV_TIMEOUT if a peer's partial did not
-                              arrive within one second (the merge is then skipped) */
+  uint32_t* status;        /* optional device word: PD_DEV_TIMEOUT if a peer's rows did not arrive
+                              within the wait limit (the merge is then skipped).  After that
+                              the ranks may disagree about the step: zero-fill every rank's
+                              buffer again before the next step. */
   void* stream;
+  int32_t rows_per_flag;   /* rows announced by one flag; divides rows; 0 = rows_per_batch.
+                              pd_decode_exchange needs num_q_heads / num_kv_heads here. */
+  int32_t phases;          /* 0 = the whole step; PD_EXCHANGE_SEND = only the part that stores
+                              and raises flags; PD_EXCHANGE_MERGE = only the wait-and-merge.
+                              A driver that plays several ranks on one GPU issues every rank's
+                              send before any merge, so that no kernel waits for a later one. */
+  uint64_t wait_limit_ns;  /* bound of the merge's wait per rank; 0 = one second, never more */
 } PdExchangeArgs;
 
+#define PD_EXCHANGE_SEND 1
+#define PD_EXCHANGE_MERGE 2
+
 /* Bytes of one rank's exchange buffer (256-byte aligned base expected). */
-PD_API uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim);
+PD_API uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag);
+
+/* Byte offset, inside an exchange buffer, of the partial that rank `rank` stores for the step
+ * parity `parity` (0 or 1); always a multiple of 16.  Exposes the layout for checks. */
+PD_API uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag,
+                                        int32_t parity, int32_t rank);
 
 /* One exchange step: store `local` into every rank's buffer (this rank's own included), raise
  * the flags, then merge the `world` partials that land in this rank's buffer into `out`.  Two
  * kernel launches on `stream`; all ranks must call it once per step. */
 PD_API int pd_exchange_step(const PdExchangeArgs* args);
+
+/* Decode and exchange in one: the streaming decode kernel stores every (request, kv head)
+ * unit's merged rows into all ranks' exchange buffers itself, as soon as the unit is done, and
+ * the wait-and-merge kernel is launched behind it as a programmatic dependent, so its launch
+ * overlaps the decode.  Two launches instead of decode + push + merge; nothing in the reference
+ * corresponds to it.  `decode` is as for pd_decode with kernel PD_KERNEL_STREAM or AUTO
+ * (PD_ERR_UNSUPPORTED when the streaming kernel does not serve it); its `out`, `result_f32` and
+ * `result_lse` may all be NULL (the merged result goes to `exchange->out`).  `exchange->local`
+ * is not used; rows, head_dim and rows_per_batch must match the decode
+ * (rows = batch * num_q_heads) and rows_per_flag must be num_q_heads / num_kv_heads. */
+PD_API int pd_decode_exchange(const PdDecodeArgs* decode, const PdExchangeArgs* exchange);
 
 /* Failure-path self-test with no counterpart in the reference: runs the kernels' bounded
  * mbarrier wait on a barrier nothing ever completes.  After `limit_ns` (at most one second) the

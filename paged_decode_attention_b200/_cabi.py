@@ -16,7 +16,7 @@ from .config import KV_CODE
 
 _PKG = pathlib.Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libpaged_decode_b200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 KERNEL_CODE = {"auto": 0, "simple": 1, "stream": 2}
 KERNEL_NAME = {1: "simple", 2: "stream"}
@@ -46,7 +46,7 @@ class PdDecodeArgs(ctypes.Structure):
         ("max_seq_len", _c_i32),
         ("workspace", _c_vp), ("workspace_bytes", _c_u64),
         ("result_f32", _c_vp), ("result_lse", _c_vp),
-        ("status", _c_vp), ("stream", _c_vp),
+        ("status", _c_vp), ("stream", _c_vp), ("flags", ctypes.c_uint32),
     ]
 
 
@@ -86,6 +86,7 @@ class PdExchangeArgs(ctypes.Structure):
         ("local", _c_vp), ("rows", _c_i32), ("head_dim", _c_i32), ("rows_per_batch", _c_i32),
         ("out", _c_vp), ("out_stride_b", _c_i64), ("out_stride_h", _c_i64), ("io_dtype", _c_i32),
         ("result_f32", _c_vp), ("result_lse", _c_vp), ("status", _c_vp), ("stream", _c_vp),
+        ("rows_per_flag", _c_i32), ("phases", _c_i32), ("wait_limit_ns", _c_u64),
     ]
 
 
@@ -97,7 +98,10 @@ class PdGatherArgs(ctypes.Structure):
 EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
            "pd_workspace_bytes", "pd_select_kernel", "pd_pick_num_splits", "pd_merge", "pd_gather",
            "pd_decode_static", "pd_cache_write", "pd_selftest_bounded_wait", "pd_exchange_bytes",
-           "pd_exchange_step")
+           "pd_exchange_step", "pd_exchange_part_offset", "pd_decode_exchange", "pd_counter_bytes")
+
+FLAG_COUNTERS_ZERO = 1
+EXCHANGE_SEND, EXCHANGE_MERGE = 1, 2
 
 STATIC_SCRATCH_BYTES = 8 << 20
 ERR_TOO_LARGE = -5
@@ -141,7 +145,13 @@ def load() -> ctypes.CDLL:
     lib.pd_gather.restype = ctypes.c_int
     lib.pd_gather.argtypes = [ctypes.POINTER(PdGatherArgs)]
     lib.pd_exchange_bytes.restype = _c_u64
-    lib.pd_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32]
+    lib.pd_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32, _c_i32]
+    lib.pd_exchange_part_offset.restype = _c_u64
+    lib.pd_exchange_part_offset.argtypes = [_c_i32] * 6
+    lib.pd_decode_exchange.restype = ctypes.c_int
+    lib.pd_decode_exchange.argtypes = [ctypes.POINTER(PdDecodeArgs), ctypes.POINTER(PdExchangeArgs)]
+    lib.pd_counter_bytes.restype = ctypes.c_int
+    lib.pd_counter_bytes.argtypes = [ctypes.POINTER(PdDecodeArgs), ctypes.POINTER(_c_u64)]
     lib.pd_exchange_step.restype = ctypes.c_int
     lib.pd_exchange_step.argtypes = [ctypes.POINTER(PdExchangeArgs)]
     lib.pd_selftest_bounded_wait.restype = ctypes.c_int

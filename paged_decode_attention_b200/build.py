@@ -17,7 +17,8 @@ import time
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libpaged_decode_b200.so"
-SOURCES = ("pd_api.cu", "pd_stream.cu")
+SOURCES = ("pd_api.cu", "pd_stream.cu", "pd_stream_f16.cu", "pd_stream_bf16.cu", "pd_stream_e5m2.cu",
+           "pd_stream_e5m2_scaled.cu", "pd_stream_i8.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -58,11 +59,14 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
             sys.stderr.write(out)
         if proc.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
-    link = [_nvcc(), "-shared", "-o", str(LIB), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    # link beside the target and rename: a reader never sees a half-written library
+    fresh = LIB.with_suffix(".so.new")
+    link = [_nvcc(), "-shared", "-o", str(fresh), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(link, check=True)
     # date the library at the start of the build: a source edited while the compiler ran is then
     # newer than the library, and the next call rebuilds instead of trusting a stale file
-    os.utime(LIB, (started, started))
+    os.utime(fresh, (started, started))
+    os.replace(fresh, LIB)
     return LIB
 
 

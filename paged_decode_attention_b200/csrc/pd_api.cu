@@ -30,11 +30,11 @@ static bool aligned(const void* p, uintptr_t a) { return ((uintptr_t)p % a) == 0
 static int elem_bytes(int kv) { return (kv == PD_KV_F16 || kv == PD_KV_BF16) ? 2 : 1; }
 
 // Checks everything that can be checked without touching the device.
-int validate(const PdDecodeArgs* a) {
+int validate(const PdDecodeArgs* a, bool need_output) {
   if (!a) return PD_ERR_INVALID_ARG;
   if (!a->q || !a->k_cache || !a->v_cache || !a->block_table || !a->seq_lens)
     return PD_ERR_INVALID_ARG;
-  if (!a->out && !a->result_f32) return PD_ERR_INVALID_ARG;
+  if (need_output && !a->out && !a->result_f32) return PD_ERR_INVALID_ARG;
   if ((a->result_f32 == nullptr) != (a->result_lse == nullptr)) return PD_ERR_INVALID_ARG;
   if (a->batch < 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->head_dim <= 0)
     return PD_ERR_INVALID_ARG;
@@ -265,6 +265,20 @@ int pd_workspace_bytes(const PdDecodeArgs* args, uint64_t* bytes) {
   return PD_OK;
 }
 
+int pd_counter_bytes(const PdDecodeArgs* args, uint64_t* bytes) {
+  if (!bytes) return PD_ERR_INVALID_ARG;
+  *bytes = 0;
+  const int rc = validate(args);
+  if (rc != PD_OK) return rc;
+  const int kernel = select_kernel(args);
+  if (kernel < 0) return kernel;
+  if (kernel != PD_KERNEL_STREAM) return PD_OK;
+  const int sms = resolve_sm_count(args);
+  if (sms <= 0) return PD_ERR_CUDA;
+  *bytes = stream_counter_bytes(args, sms);
+  return PD_OK;
+}
+
 int pd_decode(const PdDecodeArgs* args) {
   const int rc = validate(args);
   if (rc != PD_OK) return rc;
@@ -436,43 +450,123 @@ int pd_cache_write(const PdCacheWriteArgs* a) {
   return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
-uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim) {
-  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0) return 0;
-  return exchange_bytes(world, (int64_t)rows * (head_dim + 1));
+static int exchange_units(const PdExchangeArgs* a) {
+  const int per = a->rows_per_flag > 0 ? a->rows_per_flag : a->rows_per_batch;
+  return per > 0 && a->rows % per == 0 ? a->rows / per : -1;
 }
 
-int pd_exchange_step(const PdExchangeArgs* a) {
-  if (!a || !a->peer_bufs || !a->local) return PD_ERR_INVALID_ARG;
+uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag) {
+  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0 || rows_per_flag <= 0 || rows % rows_per_flag)
+    return 0;
+  return exchange_bytes(world, (int64_t)rows * (head_dim + 1), rows / rows_per_flag);
+}
+
+uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag,
+                                 int32_t parity, int32_t rank) {
+  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0 || rows_per_flag <= 0 || rows % rows_per_flag ||
+      parity < 0 || parity > 1 || rank < 0 || rank >= world)
+    return 0;
+  return exchange_part_offset(world, (int64_t)rows * (head_dim + 1), rows / rows_per_flag, parity, rank);
+}
+
+static int check_exchange(const PdExchangeArgs* a, PeerPointers& peers) {
+  if (!a || !a->peer_bufs) return PD_ERR_INVALID_ARG;
   if (a->world <= 0 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) return PD_ERR_INVALID_ARG;
   if (a->rows <= 0 || a->head_dim <= 0 || a->rows_per_batch <= 0) return PD_ERR_INVALID_ARG;
-  if (!a->out && !a->result_f32) return PD_ERR_INVALID_ARG;
+  if (exchange_units(a) <= 0) return PD_ERR_INVALID_ARG;
+  if (a->phases < 0 || a->phases > (PD_EXCHANGE_SEND | PD_EXCHANGE_MERGE)) return PD_ERR_INVALID_ARG;
+  if (a->wait_limit_ns > kExchangeWaitNs) return PD_ERR_INVALID_ARG;
+  const bool merging = a->phases == 0 || (a->phases & PD_EXCHANGE_MERGE);
+  if (merging && !a->out && !a->result_f32) return PD_ERR_INVALID_ARG;
   if (a->io_dtype != PD_IO_F16 && a->io_dtype != PD_IO_BF16) return PD_ERR_INVALID_ARG;
-  if (!aligned(a->local, 16)) return PD_ERR_UNSUPPORTED;
-  PeerPointers peers;
   for (int r = 0; r < kMaxRanks; ++r) peers.buf[r] = nullptr;
   for (int r = 0; r < a->world; ++r) {
     if (!a->peer_bufs[r] || !aligned(a->peer_bufs[r], 256)) return PD_ERR_INVALID_ARG;
     peers.buf[r] = (unsigned char*)a->peer_bufs[r];
   }
-  const int64_t n = (int64_t)a->rows * (a->head_dim + 1);
-  const cudaStream_t st = (cudaStream_t)a->stream;
-  exchange_push_kernel<<<a->world, 256, 0, st>>>(a->local, peers, a->world, a->rank, n);
-  if (cudaGetLastError() != cudaSuccess) return PD_ERR_CUDA;
+  return PD_OK;
+}
+
+// The wait-and-merge launch; `dependent` makes it a programmatic dependent of the kernel ahead
+// of it in the stream (its CTAs may be placed while that kernel still runs).
+static int launch_exchange_merge(const PdExchangeArgs* a, const PeerPointers& peers, bool dependent) {
   ExchangeMergeParams m;
   m.buf = peers.buf[a->rank];
   m.world = a->world;
   m.rows = a->rows;
   m.d = a->head_dim;
   m.rows_per_batch = a->rows_per_batch;
+  m.rows_per_flag = a->rows_per_flag > 0 ? a->rows_per_flag : a->rows_per_batch;
   m.out = a->out;
   m.dst_sb = a->out_stride_b;
   m.dst_sh = a->out_stride_h;
   m.res_o = a->result_f32;
   m.res_lse = a->result_lse;
   m.status = a->status;
-  if (a->io_dtype == PD_IO_BF16) exchange_merge_kernel<true><<<a->rows, 128, 0, st>>>(m);
-  else exchange_merge_kernel<false><<<a->rows, 128, 0, st>>>(m);
-  return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+  m.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : kExchangeWaitNs;
+  m.after_primary = dependent ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a->rows);
+  cfg.blockDim = dim3(128);
+  cfg.stream = (cudaStream_t)a->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  const cudaError_t e = a->io_dtype == PD_IO_BF16 ? cudaLaunchKernelEx(&cfg, exchange_merge_kernel<true>, m)
+                                                  : cudaLaunchKernelEx(&cfg, exchange_merge_kernel<false>, m);
+  return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
+}
+
+int pd_exchange_step(const PdExchangeArgs* a) {
+  PeerPointers peers;
+  const int rc = check_exchange(a, peers);
+  if (rc != PD_OK) return rc;
+  const bool send = a->phases == 0 || (a->phases & PD_EXCHANGE_SEND);
+  const bool merge = a->phases == 0 || (a->phases & PD_EXCHANGE_MERGE);
+  if (send) {
+    if (!a->local) return PD_ERR_INVALID_ARG;
+    if (!aligned(a->local, 16)) return PD_ERR_UNSUPPORTED;
+    const int64_t n = (int64_t)a->rows * (a->head_dim + 1);
+    exchange_push_kernel<<<a->world, 256, 0, (cudaStream_t)a->stream>>>(a->local, peers, a->world, a->rank, n,
+                                                                         exchange_units(a));
+    if (cudaGetLastError() != cudaSuccess) return PD_ERR_CUDA;
+  }
+  return merge ? launch_exchange_merge(a, peers, false) : PD_OK;
+}
+
+int pd_decode_exchange(const PdDecodeArgs* d, const PdExchangeArgs* x) {
+  const int rc = validate(d, false);
+  if (rc != PD_OK) return rc;
+  PeerPointers peers;
+  const int xrc = check_exchange(x, peers);
+  if (xrc != PD_OK) return xrc;
+  if (d->kernel == PD_KERNEL_SIMPLE) return PD_ERR_UNSUPPORTED;
+  if (d->num_q_heads % d->num_kv_heads) return PD_ERR_INVALID_ARG;
+  if (x->rows != d->batch * d->num_q_heads || x->head_dim != d->head_dim || x->rows_per_batch != d->num_q_heads ||
+      x->rows_per_flag != d->num_q_heads / d->num_kv_heads || x->stream != d->stream)
+    return PD_ERR_INVALID_ARG;
+  const int why = stream_supports(d);
+  if (why != PD_OK) return why;
+  const int sms = resolve_sm_count(d);
+  if (sms <= 0) return PD_ERR_CUDA;
+  const bool send = x->phases == 0 || (x->phases & PD_EXCHANGE_SEND);
+  const bool merge = x->phases == 0 || (x->phases & PD_EXCHANGE_MERGE);
+  if (send) {
+    PushTargets push;
+    push.peers = peers;
+    push.world = x->world;
+    push.rank = x->rank;
+    push.rows = x->rows;
+    push.units = d->batch * d->num_kv_heads;
+    Params p;
+    fill_params(d, p);
+    const int drc = stream_run(d, p, sms, &push);
+    if (drc != PD_OK) return drc;
+  }
+  // as a programmatic dependent only directly behind the decode kernel it belongs to
+  return merge ? launch_exchange_merge(x, peers, send) : PD_OK;
 }
 
 }  // extern "C"

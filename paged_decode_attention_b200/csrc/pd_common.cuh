@@ -74,6 +74,20 @@ __device__ __forceinline__ int lookup_block(const Params& p, int b, int page_idx
   return blk;
 }
 
+// Length of request b as every kernel uses it: negative lengths count as zero, and a length
+// beyond what the block-table row can name (max_blocks * page tokens) is cut there with
+// PD_DEV_BAD_BLOCK raised, so a stale or oversized length never indexes past the row.
+__device__ __forceinline__ int clamp_len(const Params& p, int b) {
+  int len = __ldg(p.seq_lens + b);
+  const long long cap = (long long)p.max_blocks * p.page;
+  if (len < 0) len = 0;
+  if (len > cap) {
+    if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
+    len = (int)cap;
+  }
+  return len;
+}
+
 // fp16 value of a stored element, exact for every kv dtype except bf16 (rounded to nearest).
 template <int KV>
 struct Stored;

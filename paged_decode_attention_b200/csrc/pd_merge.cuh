@@ -67,7 +67,7 @@ gather_kernel(const Params p, __half* __restrict__ k_dense, __half* __restrict__
   float kf[EPL], vf[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) kf[e] = vf[e] = 0.f;
-  if (s < __ldg(p.seq_lens + b)) {
+  if (s < clamp_len(p, b)) {
     const int blk = lookup_block(p, b, s / p.page);
     if (blk >= 0) {
       const int slot = s % p.page;

@@ -35,7 +35,7 @@ simple_decode_kernel(const Params p) {
   const int split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int seq_len = __ldg(p.seq_lens + b);
+  const int seq_len = clamp_len(p, b);
   int lo, hi;
   split_range(seq_len, split, p.num_splits, p.block_n, lo, hi);
 

@@ -3,6 +3,7 @@
 // point pd_decode_static and the bounded-wait self-test.
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -10,6 +11,17 @@
 #include "pd_stream_kernel.cuh"
 
 namespace pd {
+
+// One translation unit per page element type holds that type's kernel instantiations.
+#define PD_STREAM_LAUNCHER(name)                                                              \
+  cudaError_t name(int head_dim, int hb, const StreamParams& sp, const CUtensorMap& mk,      \
+                   const CUtensorMap& mv, int grid, uint32_t smem, cudaStream_t st)
+PD_STREAM_LAUNCHER(stream_launch_f16);
+PD_STREAM_LAUNCHER(stream_launch_bf16);
+PD_STREAM_LAUNCHER(stream_launch_e5m2);
+PD_STREAM_LAUNCHER(stream_launch_e5m2_scaled);
+PD_STREAM_LAUNCHER(stream_launch_i8);
+#undef PD_STREAM_LAUNCHER
 
 // ---------------------------------------------------------------------------------------------
 // host side
@@ -23,7 +35,7 @@ static int head_block(int hkv) {
 }
 
 struct Shape {
-  int hb, nhb, wpc, splits, nvseq, stage_bytes, threads;
+  int hb, nhb, wpc, splits, nvseq, stage_bytes;
   bool scaled;
 };
 
@@ -44,7 +56,6 @@ static Shape derive(const PdDecodeArgs* a) {
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   // a tile of K (or V) is hb heads x 16 tokens x the row, whatever pieces the row is moved in
   s.stage_bytes = 2 * s.hb * kTileTokens * a->head_dim * eb + (s.scaled ? 2048 : 0);
-  s.threads = s.wpc * (s.hb + 1) * 32;
   return s;
 }
 
@@ -134,6 +145,10 @@ uint64_t stream_workspace_bytes(const PdDecodeArgs* a, int sm_count) {
   return workspace_layout(a, derive(a), sm_count).total;
 }
 
+uint64_t stream_counter_bytes(const PdDecodeArgs* a, int sm_count) {
+  return workspace_layout(a, derive(a), sm_count).ticket_bytes;
+}
+
 // ---- tensor maps --------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -202,60 +217,13 @@ static bool get_tensor_map(const MapKey& k, CUtensorMap* out) {
   return true;
 }
 
-template <int KV, int D, int HB, bool SCALED, int NG, int WPC>
-static cudaError_t launch_wpc(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                              int grid, uint32_t smem, cudaStream_t st) {
-  auto* kern = stream_decode_kernel<KV, D, HB, SCALED, NG, WPC>;
-  static bool configured[64] = {};  // per device: the opt-in shared-memory limit has been raised
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorInvalidDevice;
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
-  kern<<<grid, WPC * (HB + 1) * 32, smem, st>>>(sp, mk, mv);
-  return cudaGetLastError();
-}
-
-template <int KV, int D, int HB, bool SCALED, int NG>
-static cudaError_t launch_ng(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                             int grid, uint32_t smem, cudaStream_t st) {
-  if constexpr (D == 256) {
-    static_assert(HB <= 4, "head_dim 256 runs at most four heads per block");
-    return launch_wpc<KV, D, HB, SCALED, NG, 4 / HB>(sp, mk, mv, grid, smem, st);
-  } else {
-    return launch_wpc<KV, D, HB, SCALED, NG, base_workers_per_cta(HB)>(sp, mk, mv, grid, smem, st);
-  }
-}
-
-// groups of up to 8 query heads fit one 8-wide n-tile, up to 16 need two
-template <int KV, int D, int HB, bool SCALED>
-static cudaError_t launch_one(const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                              int grid, uint32_t smem, cudaStream_t st) {
-  return sp.p.group <= 8 ? launch_ng<KV, D, HB, SCALED, 1>(sp, mk, mv, grid, smem, st)
-                         : launch_ng<KV, D, HB, SCALED, 2>(sp, mk, mv, grid, smem, st);
-}
-
-template <int KV, int D, bool SCALED>
-static cudaError_t launch_hb(int hb, const StreamParams& sp, const CUtensorMap& mk, const CUtensorMap& mv,
-                             int grid, uint32_t smem, cudaStream_t st) {
-  switch (hb) {
-    case 8:
-      if constexpr (D != 256) return launch_one<KV, D, 8, SCALED>(sp, mk, mv, grid, smem, st);
-      else return cudaErrorInvalidValue;
-    case 4: return launch_one<KV, D, 4, SCALED>(sp, mk, mv, grid, smem, st);
-    case 2: return launch_one<KV, D, 2, SCALED>(sp, mk, mv, grid, smem, st);
-    default: return launch_one<KV, D, 1, SCALED>(sp, mk, mv, grid, smem, st);
-  }
-}
-
 // Fills the kernel's parameter block for scratch at `scratch`, clears the arrival counters on the
 // stream and launches the instantiation that serves the arguments.  Shared by pd_decode and
 // pd_decode_static, which differ only in where the scratch lives and how the tensor maps are made.
 static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s, const SmemPlan& sm,
                          const WorkspaceLayout& wl, char* scratch, const CUtensorMap& mk,
-                         const CUtensorMap& mv, int sm_count) {
+                         const CUtensorMap& mv, int sm_count, bool counters_zero = false,
+                         const PushTargets* push = nullptr) {
   StreamParams sp;
   sp.p = p;
   sp.p.num_splits = s.splits;
@@ -272,35 +240,22 @@ static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s,
   sp.prefix_off = sm.prefix_off;
   sp.tickets = (int32_t*)(scratch + wl.ticket_off);
   sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
+  if (push) sp.push = *push;
+  else memset(&sp.push, 0, sizeof(sp.push));
 
   const cudaStream_t st = (cudaStream_t)a->stream;
-  // the arrival counters of the in-kernel merge start at zero
-  if (cudaMemsetAsync(sp.tickets, 0, wl.ticket_bytes, st) != cudaSuccess) return PD_ERR_CUDA;
+  // The arrival counters of the in-kernel merge start at zero.  Every kernel leaves them at
+  // zero, so a caller that vouches for a workspace it cleared once skips the memset node.
+  if (!counters_zero && cudaMemsetAsync(sp.tickets, 0, wl.ticket_bytes, st) != cudaSuccess) return PD_ERR_CUDA;
   cudaError_t e;
-  if (a->kv_dtype == PD_KV_F16) {
-    e = a->head_dim == 128 ? launch_hb<PD_KV_F16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 256 ? launch_hb<PD_KV_F16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 64 ? launch_hb<PD_KV_F16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                          : launch_hb<PD_KV_F16, 32, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else if (a->kv_dtype == PD_KV_BF16) {
-    e = a->head_dim == 128 ? launch_hb<PD_KV_BF16, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 256 ? launch_hb<PD_KV_BF16, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 64 ? launch_hb<PD_KV_BF16, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                          : launch_hb<PD_KV_BF16, 32, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else if (a->kv_dtype == PD_KV_E5M2) {
-    if (a->head_dim == 128)
-      e = s.scaled ? launch_hb<PD_KV_E5M2, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                   : launch_hb<PD_KV_E5M2, 128, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-    else if (a->head_dim == 256)
-      e = s.scaled ? launch_hb<PD_KV_E5M2, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                   : launch_hb<PD_KV_E5M2, 256, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-    else
-      e = s.scaled ? launch_hb<PD_KV_E5M2, 64, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                   : launch_hb<PD_KV_E5M2, 64, false>(s.hb, sp, mk, mv, sm_count, sm.total, st);
-  } else {
-    e = a->head_dim == 128 ? launch_hb<PD_KV_I8, 128, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-        : a->head_dim == 256 ? launch_hb<PD_KV_I8, 256, true>(s.hb, sp, mk, mv, sm_count, sm.total, st)
-                           : launch_hb<PD_KV_I8, 64, true>(s.hb, sp, mk, mv, sm_count, sm.total, st);
+  switch (a->kv_dtype) {
+    case PD_KV_F16: e = stream_launch_f16(a->head_dim, s.hb, sp, mk, mv, sm_count, sm.total, st); break;
+    case PD_KV_BF16: e = stream_launch_bf16(a->head_dim, s.hb, sp, mk, mv, sm_count, sm.total, st); break;
+    case PD_KV_E5M2:
+      e = s.scaled ? stream_launch_e5m2_scaled(a->head_dim, s.hb, sp, mk, mv, sm_count, sm.total, st)
+                   : stream_launch_e5m2(a->head_dim, s.hb, sp, mk, mv, sm_count, sm.total, st);
+      break;
+    default: e = stream_launch_i8(a->head_dim, s.hb, sp, mk, mv, sm_count, sm.total, st); break;
   }
   return e == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
@@ -310,7 +265,7 @@ static MapKey map_key(const PdDecodeArgs* a, const Shape& s, const void* base) {
                 a->block_size, a->num_kv_heads, a->num_blocks, s.hb, a->kv_dtype};
 }
 
-int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
+int stream_run(const PdDecodeArgs* a, Params& p, int sm_count, const PushTargets* push) {
   const Shape s = derive(a);
   SmemPlan sm;
   if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
@@ -319,7 +274,8 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count) {
   CUtensorMap mk, mv;
   if (!get_tensor_map(map_key(a, s, a->k_cache), &mk) || !get_tensor_map(map_key(a, s, a->v_cache), &mv))
     return PD_ERR_CUDA;
-  return launch_stream(a, p, s, sm, wl, (char*)a->workspace, mk, mv, sm_count);
+  return launch_stream(a, p, s, sm, wl, (char*)a->workspace, mk, mv, sm_count,
+                       (a->flags & PD_FLAG_COUNTERS_ZERO) != 0, push);
 }
 
 // ---------------------------------------------------------------------------------------------

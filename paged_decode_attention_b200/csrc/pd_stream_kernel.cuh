@@ -39,6 +39,7 @@
 #include <cuda.h>
 
 #include "pd_common.cuh"
+#include "pd_exchange_layout.cuh"
 
 namespace pd {
 
@@ -85,6 +86,10 @@ struct StreamParams {
   uint32_t bar_off, meta_off, misc_off, prefix_off;
   int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
   uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
+  // KV-range-sharded runs: where every finished (request, kv head) unit is also stored, on every
+  // rank of the group (push.world == 0 otherwise).  Every unit then goes through the in-kernel
+  // merge, which is the one place that delivers final rows.
+  PushTargets push;
 };
 
 // Where the TMA swizzle puts 16-byte chunk `chunk` of token row `token`: the 128-byte mode
@@ -137,7 +142,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Waits for a barrier phase for at most kWaitLimitNs.  Returns false (after raising the CTA's
 // abort flag and PD_DEV_TIMEOUT) when it gives up or when another warp already aborted.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t* status,
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t* status,
                                             volatile int* abort_flag, bool heed_abort,
                                             unsigned long long limit_ns = kWaitLimitNs) {
   const unsigned long long t0 = global_timer_ns();
@@ -281,17 +286,6 @@ __device__ __forceinline__ uint32_t cvt_pair(uint32_t w, bool upper) {
 struct VseqInfo {
   int hb, b, split, lo, hi;
 };
-
-__device__ __forceinline__ int clamp_len(const Params& p, int b) {
-  int len = __ldg(p.seq_lens + b);
-  const long long cap = (long long)p.max_blocks * p.page;
-  if (len < 0) len = 0;
-  if (len > cap) {
-    if (p.status) atomicOr(p.status, PD_DEV_BAD_BLOCK);
-    len = (int)cap;
-  }
-  return len;
-}
 
 __device__ __forceinline__ VseqInfo vseq_info(const StreamParams& sp, int v) {
   VseqInfo i;
@@ -667,7 +661,8 @@ template <int KV, int D>
 __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, int per, int v0,
                                            int splits, int hg, int head_in_block, int b, int kvh,
                                            int lane, int rslot0 = 0, int rn = 0, int rstride = 1,
-                                           int dst_slot = -1) {
+                                           int dst_slot = -1, const PushTargets* push = nullptr,
+                                           uint32_t step = 0) {
   // Default: merge every segment the schedule gives the unit and write the final rows.  With
   // rn > 0 the inputs are instead the rn slots rslot0, rslot0 + rstride, ...; with dst_slot >= 0
   // the result goes back into that slot as a normalised partial (first level of a deep merge).
@@ -761,8 +756,32 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
       }
       if (dst32) *reinterpret_cast<float4*>(dst32 + col) = make_float4(x0, x1, x2, x3);
     }
-    if (p.res_o && c == 0) p.res_lse[(int64_t)b * p.hq + hq] = denom > 0.f ? m + log2f(denom) : -INFINITY;
+    const float lse_out = denom > 0.f ? m + log2f(denom) : -INFINITY;
+    if (p.res_o && c == 0) p.res_lse[(int64_t)b * p.hq + hq] = lse_out;
+    if (push) {
+      // the same row into this rank's slot of every rank's exchange buffer (plain peer stores)
+      const int64_t n = (int64_t)push->rows * (D + 1);
+      const int64_t grow = (int64_t)b * p.hq + hq;
+      for (int r = 0; r < push->world; ++r) {
+        float* part = exchange_part(push->peers.buf[r], push->world, n, push->units, step & 1u, push->rank);
+#pragma unroll
+        for (int j = 0; j < J; ++j)
+          *reinterpret_cast<float4*>(part + grow * D + 16 * j + 4 * c) =
+              make_float4(acc[j][0] * inv, acc[j][1] * inv, acc[j][2] * inv, acc[j][3] * inv);
+        if (c == 0) part[(int64_t)push->rows * D + grow] = lse_out;
+      }
+    }
   }
+}
+
+// After a unit's rows went to every rank (merge_unit with push): make them visible system-wide,
+// then lane r raises the unit's flag in rank r's buffer.
+__device__ __forceinline__ void publish_unit(const PushTargets& push, uint32_t step, int unit, int lane) {
+  __threadfence_system();
+  __syncwarp();
+  if (lane < push.world)
+    store_release_sys(exchange_flag(push.peers.buf[lane], push.world, push.units, step & 1u, push.rank, unit),
+                      step + 1u);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -770,7 +789,7 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
 // ---------------------------------------------------------------------------------------------
 template <int KV, int D, int HB, bool SCALED, int NG, int WPC>
 __global__ void __launch_bounds__(WPC * (HB + 1) * 32, 1)
-stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
+stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
@@ -798,9 +817,15 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
     const VseqInfo i = vseq_info(sp, v);
     prefix[v + 1] = i.hi > i.lo ? (i.hi - i.lo + kTileTokens - 1) / kTileTokens : 0;
   }
+  // a cross-rank merge launched as a programmatic dependent may start now (a no-op otherwise)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const bool pushing = sp.push.world > 0;
+  volatile uint32_t* push_step = reinterpret_cast<volatile uint32_t*>(abort_flag + 2);
   if (tid == 0) {
     prefix[0] = 0;
     *abort_flag = 0;
+    // step counter of this rank's exchange buffer: its parity names the slots of this step
+    *push_step = pushing ? *reinterpret_cast<volatile uint32_t*>(sp.push.peers.buf[sp.push.rank]) : 0u;
   }
   if (role == HB && lane == 0) {
     for (int s = 0; s < nstage; ++s) {
@@ -843,7 +868,7 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
   // A small batch of short requests (fewer virtual sequences than workers, none longer than
   // kWholeTiles tiles) is dealt out whole, one request per worker, spread over the CTAs first:
   // every output row is then written directly, with no partial, ticket or merge on the way.
-  if (sp.splits == 1 && nv <= workers && *longest <= kWholeTiles) {
+  if (sp.splits == 1 && nv <= workers && *longest <= kWholeTiles && !pushing) {
     const int mine = wl * gridDim.x + blockIdx.x;
     g0 = mine < nv ? prefix[mine] : total;
     g1 = mine < nv ? prefix[mine + 1] : total;
@@ -859,6 +884,22 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
           if (p.res_o) p.res_o[((int64_t)b * p.hq + h) * D + d] = 0.f;
         }
         if (p.res_o) p.res_lse[(int64_t)b * p.hq + h] = -INFINITY;
+      }
+      if (pushing) {
+        const uint32_t step = *push_step;
+        const int64_t n = (int64_t)sp.push.rows * (D + 1);
+        for (int r = 0; r < sp.push.world; ++r) {
+          float* part = exchange_part(sp.push.peers.buf[r], sp.push.world, n, sp.push.units, step & 1u, sp.push.rank);
+          for (int h = hb * HB * p.group; h < (hb + 1) * HB * p.group; ++h) {
+            for (int d = 0; d < D; ++d) part[((int64_t)b * p.hq + h) * D + d] = 0.f;
+            part[(int64_t)sp.push.rows * D + (int64_t)b * p.hq + h] = -INFINITY;
+          }
+        }
+        __threadfence_system();
+        for (int r = 0; r < sp.push.world; ++r)
+          for (int kh = hb * HB; kh < (hb + 1) * HB; ++kh)
+            store_release_sys(exchange_flag(sp.push.peers.buf[r], sp.push.world, sp.push.units, step & 1u,
+                                            sp.push.rank, b * p.hkv + kh), step + 1u);
       }
     }
   }
@@ -956,7 +997,7 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
     const int vend = prefix[v + 1];
     const int seg_end = g1 < vend ? g1 : vend;
     int j = g - prefix[v];
-    const bool whole = (j == 0) && (seg_end == vend) && (sp.splits == 1);
+    const bool whole = (j == 0) && (seg_end == vend) && (sp.splits == 1) && !pushing;
     const int kvh = vi.hb * HB + role;
 
     // ---- query rows of this kv head's group as B fragments: thread (g, t) holds head g (+8 per
@@ -1028,6 +1069,19 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         }
         qstep[ng][0] = __shfl_sync(kFull, step, 4 * (2 * tq));
         qstep[ng][1] = __shfl_sync(kFull, step, 4 * (2 * tq + 1));
+      }
+    }
+
+    // The query rows of this worker's NEXT segment, into L1 now: their load at that segment's
+    // start is otherwise a round trip to HBM during which the warp consumes nothing (the KV
+    // stream has long pushed q out of L2).  One 128-byte line per lane.
+    if (seg_end < g1 && v + 1 < nv) {
+      const VseqInfo nx = vseq_info(sp, v + 1);
+      const int lines = (p.group * D * 2 + 127) / 128;
+      if (lane < lines) {
+        const char* nq = (const char*)p.q + 2 * ((int64_t)nx.b * p.q_sb +
+                                                 (int64_t)(nx.hb * HB + role) * p.group * p.q_sh);
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(nq + 128 * lane));
       }
     }
 
@@ -1222,7 +1276,8 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
           if (__shfl_sync(kFull, last, 0)) {
             __threadfence();
             merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
-                              kMergeRadix, -1);
+                              kMergeRadix, -1, pushing ? &sp.push : nullptr, *push_step);
+            if (pushing) publish_unit(sp.push, *push_step, vi.b * p.hkv + kvh, lane);
           }
         }
       } else {
@@ -1235,7 +1290,9 @@ stream_decode_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap 
         }
         if (__shfl_sync(kFull, last, 0)) {
           __threadfence();
-          merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane);
+          merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane, 0, 0, 1, -1,
+                            pushing ? &sp.push : nullptr, *push_step);
+          if (pushing) publish_unit(sp.push, *push_step, vi.b * p.hkv + kvh, lane);
         }
       }
     }

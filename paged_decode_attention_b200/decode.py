@@ -35,6 +35,10 @@ from .cache import PagedKVCache
 
 _ws_lock = threading.Lock()
 _ws_cache: dict[tuple[int, int], torch.Tensor] = {}
+# Buffers handed out while a CUDA graph was being captured: the graph's nodes hold their raw
+# address, so they stay referenced here for the life of the process even when a larger request
+# later replaces them in the cache.
+_ws_captured: list[torch.Tensor] = []
 
 STATS = {"decode_launches": 0}
 
@@ -63,6 +67,9 @@ def _workspace(device: torch.device, nbytes: int, stream: int | None = None) -> 
             if buf is None or buf.numel() < nbytes:
                 buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
                 _ws_cache[key] = buf
+    if torch.cuda.is_current_stream_capturing() and not any(buf is t for t in _ws_captured):
+        with _ws_lock:
+            _ws_captured.append(buf)
     return buf
 
 
@@ -78,8 +85,12 @@ def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *
                num_splits: int | None = None, sm_scale: float | None = None, kernel: str = "auto",
                result_f32: torch.Tensor | None = None, result_lse: torch.Tensor | None = None,
                status: torch.Tensor | None = None, max_seq_len: int = 0,
-               sm_count: int = 0) -> _cabi.PdDecodeArgs:
-    """Validated argument block for ``pd_decode`` (no workspace attached yet)."""
+               sm_count: int = 0, no_output: bool = False) -> _cabi.PdDecodeArgs:
+    """Validated argument block for ``pd_decode`` (no workspace attached yet).
+
+    ``no_output`` leaves ``out`` unset: only ``pd_decode_exchange`` takes such a block (its
+    result leaves through the exchange buffers).
+    """
     if q.dim() != 3:
         raise ValueError("q must be [batch, num_q_heads, head_dim]")
     b, hq, d = q.shape
@@ -101,7 +112,7 @@ def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *
         raise ValueError("cache tensors disagree with cache.shape / cache.block_size")
     args.q = q.data_ptr()
     args.q_stride_b, args.q_stride_h = q.stride(0), q.stride(1)
-    if out is not None:
+    if out is not None and not no_output:
         if out.shape != q.shape or out.dtype != q.dtype or out.stride(2) != 1:
             raise ValueError("out must match q in shape and dtype with head_dim contiguous")
         args.out = out.data_ptr()
@@ -208,18 +219,26 @@ class DecodeStep:
     def __init__(self, q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None = None, **kw):
         if not q.is_cuda:
             raise _cabi.NativeLibraryError("DecodeStep runs on CUDA tensors only; there is no CPU path")
-        self.out = torch.empty_like(q) if out is None else out
+        no_output = bool(kw.get("no_output"))
+        self.out = None if no_output else (torch.empty_like(q) if out is None else out)
         self.device = q.device
         self._keep = (q, cache, self.out, kw.get("result_f32"), kw.get("result_lse"), kw.get("status"))
         self.args = build_args(q, cache, self.out, **kw)
         need = ctypes.c_uint64(0)
-        _cabi.check(_call_on_device(self.device, _cabi.load().pd_workspace_bytes, ctypes.byref(self.args),
+        probe = self.args
+        if no_output:  # the size query wants a complete block; sizes do not depend on the pointer
+            probe = _cabi.PdDecodeArgs.from_buffer_copy(self.args)
+            probe.out = q.data_ptr()
+        _cabi.check(_call_on_device(self.device, _cabi.load().pd_workspace_bytes, ctypes.byref(probe),
                                     ctypes.byref(need)), "pd_workspace_bytes")
-        # private scratch: the step may be replayed on any stream
-        self._ws = (torch.empty(int(need.value), dtype=torch.uint8, device=self.device)
+        # Private scratch, zero-filled once: the step may be replayed on any stream, and since
+        # every call leaves the merge counters at zero and nobody else writes here, the per-call
+        # clear of the counters is not needed (PD_FLAG_COUNTERS_ZERO).
+        self._ws = (torch.zeros(int(need.value), dtype=torch.uint8, device=self.device)
                     if need.value else None)
         if self._ws is not None:
             self.args.workspace, self.args.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
+            self.args.flags |= _cabi.FLAG_COUNTERS_ZERO
         self._fn = _cabi.load().pd_decode
         self._ref = ctypes.byref(self.args)
 
@@ -232,6 +251,24 @@ class DecodeStep:
         return self.out
 
     __call__ = step
+
+    def step_at(self, q_ptr: int, out_ptr: int, block_table_ptr: int, seq_lens_ptr: int, stream: int,
+                max_seq_len: int = 0) -> None:
+        """One step with this step's buffers at new addresses, everything else as prepared.
+
+        For a serving engine that hands over fresh views of the same shapes, strides and dtypes
+        every step (its padded query and output buffers, its block table and lengths): only the
+        five addresses, the stream and the optional length bound are refreshed, nothing is
+        re-validated and no tensor object is made.  The caller vouches that the layouts are the
+        ones the step was prepared with.
+        """
+        a = self.args
+        a.q, a.out, a.block_table, a.seq_lens, a.stream = q_ptr, out_ptr, block_table_ptr, seq_lens_ptr, stream
+        a.max_seq_len = max_seq_len
+        rc = self._fn(self._ref)
+        if rc != 0:
+            _cabi.check(rc, "pd_decode")
+        STATS["decode_launches"] += 1
 
 
 # Drop-in name of the reference's entry point (pagedattn/triton_decode.py:285).

@@ -79,78 +79,112 @@ def make_kv_range_shard(name: str, rank: int, world: int, device, seed: int = 0,
 
 
 class PeerExchange:
-    """Cross-rank merge of decode partials by direct peer stores (``pd_exchange_step``).
+    """Cross-rank merge of decode partials by direct peer stores.
 
     Every rank owns one exchange buffer in torch symmetric memory, mapped into all peers.  A
-    step stores this rank's flat partial (fp32 results then lses) into every rank's buffer over
-    NVLink, raises a flag there, and merges the partials that arrive in its own buffer: two
-    small kernels of this library instead of an NCCL all-gather plus a merge.  Plain peer
-    stores only — no multicast, nothing is loaded from a peer's memory — and the wait for the
-    flags is bounded (``PD_DEV_TIMEOUT`` in ``status`` after one second).
+    step stores this rank's partial (fp32 results then lses) into every rank's buffer over
+    NVLink, raises flags there, and merges the partials that arrive in its own buffer.  Two
+    forms: ``step()`` pushes a finished flat partial with a small kernel and merges
+    (``pd_exchange_step``); ``fused_step(decode_args)`` lets the streaming decode kernel store
+    each finished (request, kv head) unit itself and launches the merge behind it as a
+    programmatic dependent (``pd_decode_exchange``).  Plain peer stores only — no multicast,
+    nothing is loaded from a peer's memory — and the wait for the flags is bounded
+    (``PD_DEV_TIMEOUT`` in ``status`` after one second).
     """
 
-    def __init__(self, local: torch.Tensor, out: torch.Tensor, group, status: torch.Tensor | None = None):
+    def __init__(self, local: torch.Tensor | None, out: torch.Tensor, group, status: torch.Tensor | None = None,
+                 rows_per_flag: int | None = None):
         import ctypes
         import os
 
+        # the exchange buffer must be reachable by plain stores only: no NVLink multicast binding
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _cabi
 
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # peer stores only
         b, hq, d = out.shape
-        if local.numel() != b * hq * (d + 1) or local.dtype != torch.float32 or not local.is_contiguous():
+        if local is not None and (local.numel() != b * hq * (d + 1) or local.dtype != torch.float32
+                                  or not local.is_contiguous()):
             raise ValueError("local must be the flat fp32 partial: B*Hq*D results then B*Hq lses")
         if not out.is_contiguous():
             raise ValueError("out must be contiguous")
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        nbytes = int(_cabi.load().pd_exchange_bytes(self.world, b * hq, d))
+        per_flag = hq if rows_per_flag is None else int(rows_per_flag)
+        nbytes = int(_cabi.load().pd_exchange_bytes(self.world, b * hq, d, per_flag))
         if nbytes == 0:
-            raise ValueError("exchange supports at most 16 ranks")
-        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=local.device)
+            raise ValueError("exchange supports at most 16 ranks and rows_per_flag must divide the rows")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=out.device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group)
-        torch.cuda.synchronize(local.device)
+        if int(getattr(self.handle, "multicast_ptr", 0) or 0) != 0:
+            raise RuntimeError("the exchange buffer was bound to an NVLink multicast object; "
+                               "set TORCH_SYMM_MEM_DISABLE_MULTICAST=1 before torch initialises symmetric memory")
+        torch.cuda.synchronize(out.device)
         dist.barrier(group)  # every buffer is zero before anybody pushes
         self._ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
         a = _cabi.PdExchangeArgs()
         a.peer_bufs = ctypes.cast(self._ptrs, ctypes.POINTER(ctypes.c_void_p))
         a.world, a.rank = self.world, self.rank
-        a.local = local.data_ptr()
-        a.rows, a.head_dim, a.rows_per_batch = b * hq, d, hq
+        if local is not None:
+            a.local = local.data_ptr()
+        a.rows, a.head_dim, a.rows_per_batch, a.rows_per_flag = b * hq, d, hq, per_flag
         a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), hq * d, d
         a.io_dtype = _cabi.IO_CODE[out.dtype]
         if status is not None:
             a.status = status.data_ptr()
         self._keep = (local, out, status)
-        self.args, self._ref, self._fn = a, ctypes.byref(a), _cabi.load().pd_exchange_step
-        self.device = local.device
+        self.args, self._ref = a, ctypes.byref(a)
+        self._step, self._fused = _cabi.load().pd_exchange_step, _cabi.load().pd_decode_exchange
+        self.device = out.device
 
     def step(self) -> None:
         from . import _cabi
 
         self.args.stream = torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._fn(self._ref)
+        rc = self._step(self._ref)
         if rc != 0:
             _cabi.check(rc, "pd_exchange_step")
+
+    def fused_step(self, decode_args) -> None:
+        """Decode + push + merge in two launches; ``decode_args`` is a prepared ``PdDecodeArgs``."""
+        import ctypes
+
+        from . import _cabi
+
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.args.stream = decode_args.stream = stream
+        rc = self._fused(ctypes.byref(decode_args), self._ref)
+        if rc != 0:
+            _cabi.check(rc, "pd_decode_exchange")
 
 
 class KVRangeShardedDecoder:
     """Decode step of one rank of a KV-range-sharded group.
 
-    ``step()`` = local decode to (fp32 partial, lse) -> one all-gather -> merge of
-    ``world`` partials into ``out``.  The partial and its lse live in one flat buffer so a
-    single collective moves both.  ``decode_fn``/``merge_fn`` default to the CUDA library;
-    host-side tests inject CPU stand-ins to exercise the plumbing over gloo.
+    ``step()`` = local decode to (fp32 partial, lse) -> exchange -> merge of ``world`` partials
+    into ``out``.  ``exchange`` picks how the partials travel: ``"nccl"`` (one all-gather of the
+    flat partial through the group's backend, then the merge kernel; the default, and the only
+    one for CPU stand-ins over gloo), ``"peer"`` (a push kernel stores it into every rank's
+    buffer, a merge kernel waits for the flags), ``"fused"`` (the decode kernel stores each
+    finished unit itself; the merge is launched behind it as a programmatic dependent).
+    ``decode_fn``/``merge_fn`` default to the CUDA library; host-side tests inject CPU
+    stand-ins to exercise the plumbing over gloo.
+
+    Call ``close()`` on every rank before ``destroy_process_group``: a captured step that
+    contains an NCCL all-gather keeps a reference on the communicator, and tearing the
+    communicator down while that graph is alive waits for it for ever.
     """
 
     def __init__(self, q: torch.Tensor, cache: PagedKVCache, group=None, kernel: str = "auto",
                  decode_fn: Callable | None = None, merge_fn: Callable | None = None,
                  exchange: str = "nccl", status: torch.Tensor | None = None):
-        if exchange not in ("nccl", "peer"):
-            raise ValueError("exchange must be 'nccl' (all-gather + merge) or 'peer' (direct peer stores)")
+        if exchange not in ("nccl", "peer", "fused"):
+            raise ValueError("exchange must be 'nccl' (all-gather + merge), 'peer' (push kernel + merge) "
+                             "or 'fused' (the decode kernel pushes)")
         self.q, self.cache, self.group, self.kernel = q, cache, group, kernel
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.exchange = exchange
         b, hq, d = q.shape
         self.n_o = b * hq * d
         self.local = torch.empty(self.n_o + b * hq, dtype=torch.float32, device=q.device)
@@ -161,21 +195,29 @@ class KVRangeShardedDecoder:
         self.lses = self.gathered[:, self.n_o:].view(self.world, b, hq)
         self.out = torch.empty_like(q)
         self.graph = None
+        self._decode_step = None
         if decode_fn is None:
             from .decode import DecodeStep, MergeStep
 
-            decode_step = DecodeStep(q, cache, None, result_f32=self.f32, result_lse=self.lse, kernel=kernel)
+            fused = exchange == "fused" and dist.is_initialized()
+            self._decode_step = DecodeStep(q, cache, None, kernel=kernel, status=status, no_output=True) if fused \
+                else DecodeStep(q, cache, None, result_f32=self.f32, result_lse=self.lse, kernel=kernel)
             merge_step = MergeStep(self.parts, self.lses, self.out)
-            decode_fn = lambda *_: decode_step.step()
+            decode_fn = lambda *_: self._decode_step.step()
             merge_fn = lambda *_: merge_step.step()
         self.decode_fn, self.merge_fn = decode_fn, merge_fn
         self.launches_per_step = 2  # decode (merges its own splits), the cross-rank merge
         self.peer = None
-        if exchange == "peer" and self.world > 1:
-            self.peer = PeerExchange(self.local, self.out, group, status=status)
-            self.launches_per_step = 3  # decode, push, wait-and-merge
+        if exchange in ("peer", "fused") and dist.is_initialized():
+            group_size = hq // cache.shape.num_kv_heads
+            self.peer = PeerExchange(None if exchange == "fused" else self.local, self.out, group, status=status,
+                                     rows_per_flag=group_size if exchange == "fused" else None)
+            self.launches_per_step = 2 if exchange == "fused" else 3  # decode, [push,] wait-and-merge
 
     def _run(self) -> None:
+        if self.peer is not None and self.exchange == "fused" and self._decode_step is not None:
+            self.peer.fused_step(self._decode_step.args)
+            return
         self.decode_fn(self.q, self.cache, self.f32, self.lse, self.kernel)
         if self.peer is not None:
             self.peer.step()
@@ -187,12 +229,12 @@ class KVRangeShardedDecoder:
         self.merge_fn(self.parts, self.lses, self.out)
 
     def capture(self) -> None:
-        """Record decode -> all-gather -> merge into one CUDA graph; ``step`` then replays it.
+        """Record the whole step into one CUDA graph; ``step`` then replays it.
 
         At eight ranks a rank's slice of a long request decodes in a few tens of
-        microseconds, less than the host needs to issue the three operations; replaying a
-        graph takes the host out of the step.  Every rank of the group must call this at the
-        same point (the all-gather is captured collectively), after at least one plain step.
+        microseconds, less than the host needs to issue the operations; replaying a graph
+        takes the host out of the step.  Every rank of the group must call this at the same
+        point (an all-gather is captured collectively), after at least one plain step.
         """
         side = torch.cuda.Stream(device=self.q.device)
         side.wait_stream(torch.cuda.current_stream(self.q.device))
@@ -210,3 +252,19 @@ class KVRangeShardedDecoder:
         else:
             self._run()
         return self.out
+
+    def close(self) -> None:
+        """Waits for this rank's work and releases the captured graph.
+
+        Collective in effect, not in form: every rank must have called it before any rank
+        destroys the process group (a barrier between the two is the caller's).  Safe to call
+        twice; ``step`` falls back to host-issued launches afterwards.
+        """
+        if self.q.is_cuda:
+            torch.cuda.synchronize(self.q.device)
+        graph, self.graph = self.graph, None
+        if graph is not None:
+            graph.reset()
+            del graph
+        if self.q.is_cuda:
+            torch.cuda.synchronize(self.q.device)

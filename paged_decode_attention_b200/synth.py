@@ -72,16 +72,20 @@ def draw_lengths(name: str, gen: torch.Generator, batch: int | None = None,
 
 
 def make(name: str, device: str | torch.device = "cuda", seed: int = 0, batch: int | None = None,
-         seq_len: int | None = None, pool_blocks: int | None = None) -> tuple[torch.Tensor, PagedKVCache]:
+         seq_len: int | None = None, pool_blocks: int | None = None,
+         lengths: torch.Tensor | None = None) -> tuple[torch.Tensor, PagedKVCache]:
     """(q, cache) of workload `name` on `device`.
 
     ``batch``/``seq_len`` shrink or reshape the draw (for tests and sharding);
-    ``pool_blocks`` enlarges the pool beyond the pages in use (c1 uses 256).
+    ``pool_blocks`` enlarges the pool beyond the pages in use (c1 uses 256);
+    ``lengths`` replaces the drawn lengths altogether (one rank's requests of a batch whose
+    lengths were drawn once for all ranks).
     """
     w = WORKLOADS[name]
     dev = torch.device(device)
     host_gen = torch.Generator(device="cpu").manual_seed(seed)
-    lens = draw_lengths(name, host_gen, batch, seq_len)
+    lens = (draw_lengths(name, host_gen, batch, seq_len) if lengths is None
+            else lengths.to(torch.int32).cpu().reshape(-1))
     b = int(lens.numel())
     pages = (lens.to(torch.int64) + w.page - 1) // w.page
     used = int(pages.sum())
@@ -113,7 +117,7 @@ def make(name: str, device: str | torch.device = "cuda", seed: int = 0, batch: i
     k_cache, k_scale = pages_tensor(), scales_tensor()
     v_cache, v_scale = pages_tensor(), scales_tensor()
     order = torch.randperm(pool, generator=host_gen)[:used].to(torch.int32)
-    table = torch.zeros((b, max(1, int(pages.max()))), dtype=torch.int32)
+    table = torch.zeros((b, max(1, int(pages.max()) if b else 1)), dtype=torch.int32)
     at = 0
     for row, n in enumerate(pages.tolist()):
         table[row, :n] = order[at:at + n]

@@ -11,15 +11,24 @@ from paged_decode_attention_b200 import ModelShape, PagedKVCache
 
 # Tolerances of the parity contract: against the reference's fp32 result, the fp16 output
 # must be within 2e-3 absolute, and within 1e-2 of the largest reference value
-# (the reference's own metric, tests/test_correctness.py:28,48-51).  The 2e-3 is stated for
-# unit-scale data (q, k, v ~ N(0,1): |out| below about 2).  Where scales or short requests push
-# |out| above 1, the absolute bound grows with the largest reference value — 2e-3 * max|ref|,
-# i.e. still 0.2 % — because rounding the result to fp16 alone costs up to 2^-11 of its value
-# (1.95e-3 at |out| = 4) before any arithmetic error.
+# (the reference's own metric, tests/test_correctness.py:28,48-51).  The 2e-3 holds as it
+# stands wherever the largest reference value is below 4.  From 4 upwards rounding the result
+# to fp16 alone costs up to 1.95e-3 (half a unit in the last place of [4, 8)), so no
+# arithmetic could meet 2e-3 there; only in that range the bound grows in proportion:
+# 2e-3 * max|ref| / 2 (4e-3 at 4: the rounding plus the same 2e-3 for the arithmetic).
 ABS_TOL = 2e-3
+ABS_TOL_SCALES_FROM = 4.0
 REL_TOL = 1e-2
-# bf16 has 8 significand bits: rounding the output alone costs up to 2^-9 of its value.
+# bf16 has 8 significand bits: rounding the output alone costs up to 2^-9 of its value
+# (7.8e-3 just below 4); 1.6e-2 is that plus the arithmetic, scaled the same way from 4 upwards.
 ABS_TOL_BF16 = 1.6e-2
+
+
+def abs_tolerance(ref_f32: np.ndarray, bf16: bool = False) -> float:
+    """Absolute bound for a result whose fp32 truth is `ref_f32`."""
+    peak = float(np.abs(ref_f32).max()) if ref_f32.size else 0.0
+    base = ABS_TOL_BF16 if bf16 else ABS_TOL
+    return base if peak < ABS_TOL_SCALES_FROM else base * peak / 2.0
 
 
 def store_to_torch(a: np.ndarray, kv_dtype: str, device) -> torch.Tensor:
@@ -58,6 +67,6 @@ def errors(got: torch.Tensor, ref_f32: np.ndarray) -> tuple[float, float]:
 def assert_close(got: torch.Tensor, ref_f32: np.ndarray, bf16: bool = False, what: str = "") -> None:
     assert not torch.isnan(got.float()).any(), f"{what}: NaN in output"
     err, rel = errors(got, ref_f32)
-    tol = (ABS_TOL_BF16 if bf16 else ABS_TOL) * max(1.0, float(np.abs(ref_f32).max()) if ref_f32.size else 1.0)
+    tol = abs_tolerance(ref_f32, bf16)
     assert err <= tol, f"{what}: max-abs error {err:.3e} > {tol}"
     assert rel <= REL_TOL, f"{what}: relative error {rel:.3e} > {REL_TOL}"

@@ -4,6 +4,7 @@ dates the library at its start so that an edit made while the compiler ran is no
 from __future__ import annotations
 
 import os
+import pathlib
 import time
 
 from paged_decode_attention_b200 import build as pbuild
@@ -53,12 +54,15 @@ def test_build_dates_the_library_at_its_start(tmp_path, monkeypatch):
         (csrc / pbuild.SOURCES[0]).write_text("// edited during the build")
         return FakeProc()
 
-    def fake_run(cmd, check):  # "linking"
-        lib.write_bytes(b"linked")
+    def fake_run(cmd, check):  # "linking": to the output the command names, never straight to the library
+        out = pathlib.Path(cmd[cmd.index("-o") + 1])
+        assert out != lib, "the link must not write the library in place"
+        out.write_bytes(b"linked")
 
     monkeypatch.setattr(pbuild, "_nvcc", lambda: "nvcc")
     monkeypatch.setattr(pbuild.subprocess, "Popen", fake_popen)
     monkeypatch.setattr(pbuild.subprocess, "run", fake_run)
     pbuild.build(force=True)
-    assert lib.exists()
+    assert lib.exists() and lib.read_bytes() == b"linked"
+    assert [p.name for p in lib.parent.iterdir() if p.name.startswith(lib.name) and p != lib] == []
     assert pbuild.needs_build(), "the edit made during the build must trigger the next build"

@@ -156,3 +156,83 @@ def test_header_is_plain_c():
     r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c",
                         str(ROOT / "include" / "paged_decode.h")], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+def _header_fields(struct: str) -> list[str]:
+    header = (ROOT / "include" / "paged_decode.h").read_text()
+    body = header.split(f"typedef struct {struct} {{")[1].split(f"}} {struct};")[0]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for stmt in body.split(";"):
+        stmt = stmt.strip()
+        if not stmt:
+            continue
+        for part in stmt.split(","):
+            names.append(re.findall(r"(\w+)\s*$", part.strip())[0])
+    return names
+
+
+@pytest.mark.parametrize("struct", ["PdExchangeArgs", "PdMergeArgs", "PdCacheWriteArgs", "PdHostIO"])
+def test_other_struct_layouts_match_header_field_order(struct):
+    assert _header_fields(struct) == [f[0] for f in getattr(_cabi, struct)._fields_]
+
+
+@pytest.mark.parametrize("rows,d,per_flag", [(1, 64, 1), (6, 128, 3), (14, 64, 7), (14, 64, 14), (128, 128, 4),
+                                             (910, 1, 1)])
+@pytest.mark.parametrize("world", [1, 2, 3, 8, 16])
+def test_exchange_slots_are_16_byte_aligned_and_disjoint(world, rows, d, per_flag):
+    """A partial is rows * (d + 1) floats, odd-sized for most shapes; every (parity, rank) slot
+    must still start on a 16-byte boundary (the push copies with 16-byte stores), must not
+    overlap its neighbour and must end inside the buffer."""
+    lib = _cabi.load()
+    total = int(lib.pd_exchange_bytes(world, rows, d, per_flag))
+    assert total > 0 and total % 16 == 0
+    n_bytes = rows * (d + 1) * 4
+    offs = []
+    for parity in (0, 1):
+        for r in range(world):
+            off = int(lib.pd_exchange_part_offset(world, rows, d, per_flag, parity, r))
+            assert off % 16 == 0 and off >= 256 + 2 * world * (rows // per_flag) * 4
+            offs.append(off)
+    assert offs == sorted(offs)
+    for a, b in zip(offs, offs[1:]):
+        assert b - a >= n_bytes
+    assert offs[-1] + n_bytes <= total
+
+
+def test_exchange_sizes_reject_bad_arguments():
+    lib = _cabi.load()
+    assert lib.pd_exchange_bytes(17, 8, 64, 1) == 0       # more than 16 ranks
+    assert lib.pd_exchange_bytes(2, 9, 64, 2) == 0        # flags do not divide the rows
+    assert lib.pd_exchange_bytes(2, 8, 64, 0) == 0
+    assert lib.pd_exchange_part_offset(2, 8, 64, 1, 2, 0) == 0
+    assert lib.pd_exchange_part_offset(2, 8, 64, 1, 0, 2) == 0
+    x = _cabi.PdExchangeArgs()
+    assert lib.pd_exchange_step(ctypes.byref(x)) == -1
+    assert lib.pd_decode_exchange(None, ctypes.byref(x)) == -1
+
+
+def test_workspace_handed_out_during_capture_is_never_dropped(monkeypatch):
+    """A graph captured with a cached workspace keeps its raw address; when a larger request
+    replaces the cache entry, the old buffer must stay referenced."""
+    made = []
+
+    def fake_empty(n, dtype=None, device=None):
+        t = torch.zeros(int(n), dtype=dtype)
+        made.append(t)
+        return t
+
+    monkeypatch.setattr(pdec.torch, "empty", fake_empty)
+    monkeypatch.setattr(pdec.torch.cuda, "is_current_stream_capturing", lambda: True)
+    monkeypatch.setattr(pdec, "_ws_cache", {})
+    monkeypatch.setattr(pdec, "_ws_captured", [])
+    dev = torch.device("cuda", 0)
+    small = pdec._workspace(dev, 1000, stream=5)
+    again = pdec._workspace(dev, 2000, stream=5)
+    assert again is small and len(pdec._ws_captured) == 1
+    big = pdec._workspace(dev, 8 << 20, stream=5)
+    assert big is not small
+    assert any(t is small for t in pdec._ws_captured) and any(t is big for t in pdec._ws_captured)
+    monkeypatch.setattr(pdec.torch.cuda, "is_current_stream_capturing", lambda: False)
+    other = pdec._workspace(dev, 100, stream=6)
+    assert not any(t is other for t in pdec._ws_captured)

@@ -9,6 +9,7 @@ group of one, shuffled vs ascending tables, other model shapes — for both CUDA
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 
 import numpy as np
 import pytest
@@ -152,6 +153,47 @@ def test_bad_block_id_sets_status_and_does_not_touch_memory(kernel):
     torch.cuda.synchronize()
     assert int(status.item()) & _cabi.DEV_BAD_BLOCK
     assert not torch.isnan(out).any()
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_length_beyond_the_block_table_row_is_cut_and_flagged(kernel):
+    """A length larger than max_blocks * page cannot be served: every kernel (and the gather)
+    cuts it at the end of the block-table row, raises PD_DEV_BAD_BLOCK, gives finite output,
+    and leaves the other request's row exactly as without the bad length."""
+    case = cases.BY_NAME["llama8b_b2_s65"]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = torch.from_numpy(q_np).cuda()
+    which = kernel if kernel == "simple" else "auto"
+    clean = pda.paged_decode(q, cache, kernel=which).clone()
+    cap = cache.block_table.shape[1] * cache.block_size
+    lens = cache.seq_lens.clone()
+    lens[1] = cap + 5 * cache.block_size + 3
+    bad = dataclasses.replace(cache, seq_lens=lens)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = pda.paged_decode(q, bad, status=status, kernel=which)
+    torch.cuda.synchronize()
+    assert int(status.item()) & _cabi.DEV_BAD_BLOCK
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out[0], clean[0])
+    # the row with the oversized length equals a decode of exactly the tokens its row can name
+    lens_cap = cache.seq_lens.clone()
+    lens_cap[1] = cap
+    want = pda.paged_decode(q, dataclasses.replace(cache, seq_lens=lens_cap), kernel=which)
+    assert torch.equal(out[1], want[1])
+    # the gather applies the same cut: rows past it stay zero
+    args = _cabi.PdDecodeArgs()
+    _cabi.fill_cache_fields(args, bad)
+    st2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args.status = st2.data_ptr()
+    s_max = cap + 16
+    kd = torch.full((2, cache.shape.num_kv_heads, s_max, cache.shape.head_dim), 7.0, dtype=torch.float16, device="cuda")
+    vd = torch.full_like(kd, 7.0)
+    g = _cabi.PdGatherArgs(ctypes.pointer(args), kd.data_ptr(), vd.data_ptr(), s_max)
+    _cabi.check(_cabi.load().pd_gather(ctypes.byref(g)), "pd_gather")
+    torch.cuda.synchronize()
+    assert int(st2.item()) & _cabi.DEV_BAD_BLOCK
+    assert float(kd[1, :, cap:].abs().max()) == 0.0 and float(vd[1, :, cap:].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("kernel", KERNELS)

@@ -76,6 +76,9 @@ def _worker(rank: int, world: int, port: int, result_path: str):
         lens = [int(n) for n in cache.seq_lens.tolist()]
         if rank == 0:
             torch.save({"out": out, "q": q, "lens0": lens}, result_path)
+        dec.close()
+        dec.close()  # idempotent
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 

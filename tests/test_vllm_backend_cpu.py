@@ -75,39 +75,76 @@ def test_pure_decode_is_ours():
     assert vb._reason_to_delegate(_impl(), _meta(), _kv(), torch.zeros(4, 32, 128), None, None) == ""
 
 
+class _FakeCall:
+    def __init__(self, log):
+        self.log = log
+
+    def step_at(self, q_ptr, out_ptr, bt_ptr, sl_ptr, stream, max_seq_len=0):
+        self.log.append(dict(q=q_ptr, out=out_ptr, bt=bt_ptr, sl=sl_ptr, stream=stream, max_seq_len=max_seq_len))
+
+
+def _patch_native(monkeypatch, seen, log):
+    def fake_prepare(q, cache, out, sm_scale):
+        seen.append(dict(q=q, cache=cache, out=out, sm_scale=sm_scale))
+        return _FakeCall(log)
+
+    monkeypatch.setattr(vb, "_prepare_call", fake_prepare)
+    monkeypatch.setattr(vb, "_PREPARED", {})
+    monkeypatch.setattr(vb.torch.cuda, "current_stream", lambda dev=None: types.SimpleNamespace(cuda_stream=77))
+
+
 def test_decode_step_builds_zero_copy_views(monkeypatch):
-    seen = {}
-
-    def fake_decode(q, cache, out=None, sm_scale=None, max_seq_len=0, **kw):
-        seen.update(q=q, cache=cache, out=out, sm_scale=sm_scale, max_seq_len=max_seq_len)
-        return out
-
-    monkeypatch.setattr(vb, "paged_decode", fake_decode)
+    seen, log = [], []
+    _patch_native(monkeypatch, seen, log)
     before = dict(vb.STATS)
     kv = _kv()
     query = torch.zeros(4, 32, 128, dtype=torch.float16)   # padded to 4 tokens, 3 are real
     output = torch.zeros(4, 32 * 128, dtype=torch.float16)
     meta = _meta(n=3)
     vb._decode_step(_impl(), query, kv, meta, output)
-    c = seen["cache"]
+    c = seen[0]["cache"]
     assert c.k_cache.data_ptr() == kv.data_ptr()                      # views, not copies
     assert c.v_cache.data_ptr() == kv[:, 1].data_ptr()
     assert c.k_cache.shape == (20, 16, 8, 128) and c.k_cache.stride(0) == 2 * 16 * 8 * 128
     assert c.block_size == 16 and c.kv_dtype == "fp16" and c.k_scale is None
     assert c.block_table.shape[0] == 3 and c.seq_lens.shape[0] == 3
-    assert seen["q"].shape == (3, 32, 128) and seen["q"].data_ptr() == query.data_ptr()
-    assert seen["out"].shape == (3, 32, 128) and seen["out"].data_ptr() == output.data_ptr()
-    assert seen["sm_scale"] == pytest.approx(0.0883) and seen["max_seq_len"] == 40
+    assert seen[0]["q"].shape == (3, 32, 128) and seen[0]["q"].data_ptr() == query.data_ptr()
+    assert seen[0]["out"].shape == (3, 32, 128) and seen[0]["out"].data_ptr() == output.data_ptr()
+    assert seen[0]["sm_scale"] == pytest.approx(0.0883)
+    assert log[0] == dict(q=query.data_ptr(), out=output.data_ptr(), bt=meta.block_table.data_ptr(),
+                          sl=meta.seq_lens.data_ptr(), stream=77, max_seq_len=40)
     assert vb.STATS["decode_calls"] == before["decode_calls"] + 1
     assert vb.STATS["decode_tokens"] == before["decode_tokens"] + 3
 
 
+def test_prepared_call_is_reused_and_only_addresses_move(monkeypatch):
+    """Same layer cache and batch size: prepared once; a new query buffer only changes the
+    address handed over.  Another batch size or another layer's cache prepares anew."""
+    seen, log = [], []
+    _patch_native(monkeypatch, seen, log)
+    kv, meta, impl = _kv(), _meta(n=3), _impl()
+    q1 = torch.zeros(4, 32, 128, dtype=torch.float16)
+    q2 = torch.zeros(4, 32, 128, dtype=torch.float16)
+    out = torch.zeros(4, 32, 128, dtype=torch.float16)
+    vb._decode_step(impl, q1, kv, meta, out)
+    vb._decode_step(impl, q2, kv, meta, out)
+    assert len(seen) == 1 and len(log) == 2
+    assert log[0]["q"] == q1.data_ptr() and log[1]["q"] == q2.data_ptr()
+    vb._decode_step(impl, q1, kv, _meta(n=2), out)            # other batch size
+    vb._decode_step(impl, q1, _kv(), meta, out)               # other layer's cache
+    assert len(seen) == 3 and len(log) == 4
+    # the table is bounded
+    monkeypatch.setattr(vb, "_PREPARED_CAP", 2)
+    vb._decode_step(impl, q1, _kv(), meta, out)
+    assert len(vb._PREPARED) <= 3
+
+
 def test_bf16_cache_is_labelled(monkeypatch):
-    seen = {}
-    monkeypatch.setattr(vb, "paged_decode", lambda q, cache, **kw: seen.update(cache=cache))
+    seen, log = [], []
+    _patch_native(monkeypatch, seen, log)
     vb._decode_step(_impl(), torch.zeros(4, 32, 128, dtype=torch.bfloat16), _kv(dtype=torch.bfloat16),
                     _meta(), torch.zeros(4, 32, 128, dtype=torch.bfloat16))
-    assert seen["cache"].kv_dtype == "bf16"
+    assert seen[0]["cache"].kv_dtype == "bf16"
 
 
 def test_env_switch_off_by_default(monkeypatch):
@@ -116,7 +153,13 @@ def test_env_switch_off_by_default(monkeypatch):
 
 
 @pytest.mark.skipif(not vb.HAVE_VLLM, reason="vLLM not importable")
-def test_forward_delegates_or_serves(monkeypatch):
+@pytest.mark.parametrize("parent", ["triton", "flash"])
+def test_forward_delegates_or_serves(monkeypatch, parent):
+    if parent == "flash" and not vb.HAVE_FLASH:
+        pytest.skip("the engine's FlashAttention backend is not importable")
+    impl_cls = vb.PagedDecodeB200FlashImpl if parent == "flash" else vb.PagedDecodeB200Impl
+    parent_cls = vb.FlashAttentionImpl if parent == "flash" else vb.TritonAttentionImpl
+    backend_cls = vb.PagedDecodeB200FlashBackend if parent == "flash" else vb.PagedDecodeB200Backend
     calls = {"parent": 0, "ours": 0}
 
     def parent_forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None,
@@ -124,9 +167,9 @@ def test_forward_delegates_or_serves(monkeypatch):
         calls["parent"] += 1
         return output
 
-    monkeypatch.setattr(vb.TritonAttentionImpl, "forward", parent_forward)
+    monkeypatch.setattr(parent_cls, "forward", parent_forward)
     monkeypatch.setattr(vb, "_decode_step", lambda *a, **k: calls.__setitem__("ours", calls["ours"] + 1))
-    impl = object.__new__(vb.PagedDecodeB200Impl)
+    impl = object.__new__(impl_cls)
     for k, v in vars(_impl()).items():
         setattr(impl, k, v)
     q = torch.zeros(4, 32, 128, dtype=torch.float16)
@@ -141,7 +184,21 @@ def test_forward_delegates_or_serves(monkeypatch):
     impl.forward(None, q, None, None, _kv(d=96), _meta(), out)                     # shape gate
     assert calls == {"parent": 4, "ours": 1}
     assert vb.STATS["delegated_calls"] == delegated0 + 4
-    assert vb.PagedDecodeB200Backend.get_impl_cls() is vb.PagedDecodeB200Impl
+    assert backend_cls.get_impl_cls() is impl_cls and backend_cls.get_name() == "CUSTOM"
+    assert impl_cls.kv_axis == (0 if parent == "flash" else 1)
+
+
+def test_flash_parent_cache_views_are_the_two_dense_halves(monkeypatch):
+    """[2, NB, PAGE, H, D] (the FlashAttention backend's layout): K and V are the halves along axis 0."""
+    seen, log = [], []
+    _patch_native(monkeypatch, seen, log)
+    kv = torch.zeros((2, 20, 16, 8, 128), dtype=torch.float16)
+    impl = _impl(kv_axis=0)
+    q = torch.zeros(4, 32, 128, dtype=torch.float16)
+    vb._decode_step(impl, q, kv, _meta(), torch.zeros(4, 32, 128, dtype=torch.float16))
+    c = seen[0]["cache"]
+    assert c.k_cache.data_ptr() == kv[0].data_ptr() and c.v_cache.data_ptr() == kv[1].data_ptr()
+    assert c.k_cache.shape == (20, 16, 8, 128) and c.k_cache.is_contiguous()
 
 
 @pytest.mark.skipif(not vb.HAVE_VLLM, reason="vLLM not importable")
@@ -152,3 +209,12 @@ def test_install_registers_custom_backend(monkeypatch):
     assert vb.maybe_install_from_env() is True
     assert vb.install() == vb.QUALNAME
     assert AttentionBackendEnum.CUSTOM.get_path() == vb.QUALNAME
+    if vb.HAVE_FLASH:
+        assert vb.install(parent="flash") == vb.QUALNAME_FLASH
+        assert AttentionBackendEnum.CUSTOM.get_path() == vb.QUALNAME_FLASH
+        monkeypatch.setenv("PAGEDATTN_VLLM_PARENT", "flash")
+        assert vb.install() == vb.QUALNAME_FLASH
+        monkeypatch.delenv("PAGEDATTN_VLLM_PARENT")
+    with pytest.raises(ValueError):
+        vb.install(parent="other")
+    assert vb.install() == vb.QUALNAME
