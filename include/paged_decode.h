@@ -234,8 +234,8 @@ PD_API int pd_gather(const PdGatherArgs* args);
  * _split_reduce_kernel (pagedattn/triton_decode.py:221-240) over ranks.  Every rank owns one
  * exchange buffer of pd_exchange_bytes() bytes, zero-filled once, mapped into every peer
  * (e.g. torch symmetric memory); `peer_bufs[r]` is rank r's buffer as seen from this rank.
- * A partial arrives in pieces of `rows_per_flag` consecutive rows, each announced by its own
- * flag, so a merge can start on the rows that are there. */
+ * Every value crosses as one indivisible 8-byte word that carries the step's mark beside the
+ * float, so nothing is fenced or flagged and a merge uses each word as soon as it is there. */
 typedef struct PdExchangeArgs {
   void* const* peer_bufs;  /* host array [world]; entry [rank] is this rank's own buffer */
   int32_t world, rank;     /* world <= 16 */
@@ -248,15 +248,13 @@ typedef struct PdExchangeArgs {
   int32_t io_dtype;
   float* result_f32;       /* optional merged fp32 result [rows, head_dim] */
   float* result_lse;       /* optional merged lse [rows] */
-  uint32_t* status;        /* optional device word: PD_DEV_TIMEOUT if a peer's rows did not arrive
+  uint32_t* status;        /* optional device word: PD_DEV_TIMEOUT if a peer's words did not arrive
                               within the wait limit (the merge is then skipped).  After that
                               the ranks may disagree about the step: zero-fill every rank's
                               buffer again before the next step. */
   void* stream;
-  int32_t rows_per_flag;   /* rows announced by one flag; divides rows; 0 = rows_per_batch.
-                              pd_decode_exchange needs num_q_heads / num_kv_heads here. */
-  int32_t phases;          /* 0 = the whole step; PD_EXCHANGE_SEND = only the part that stores
-                              and raises flags; PD_EXCHANGE_MERGE = only the wait-and-merge.
+  int32_t phases;          /* 0 = the whole step; PD_EXCHANGE_SEND = only the part that stores;
+                              PD_EXCHANGE_MERGE = only the wait-and-merge.
                               A driver that plays several ranks on one GPU issues every rank's
                               send before any merge, so that no kernel waits for a later one. */
   uint64_t wait_limit_ns;  /* bound of the merge's wait per rank; 0 = one second, never more */
@@ -266,16 +264,17 @@ typedef struct PdExchangeArgs {
 #define PD_EXCHANGE_MERGE 2
 
 /* Bytes of one rank's exchange buffer (256-byte aligned base expected). */
-PD_API uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag);
+PD_API uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim);
 
 /* Byte offset, inside an exchange buffer, of the partial that rank `rank` stores for the step
- * parity `parity` (0 or 1); always a multiple of 16.  Exposes the layout for checks. */
-PD_API uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag,
-                                        int32_t parity, int32_t rank);
+ * parity `parity` (0 or 1): rows * (head_dim + 1) words of 8 bytes; always a multiple of 256.
+ * Exposes the layout for checks. */
+PD_API uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t parity,
+                                        int32_t rank);
 
-/* One exchange step: store `local` into every rank's buffer (this rank's own included), raise
- * the flags, then merge the `world` partials that land in this rank's buffer into `out`.  Two
- * kernel launches on `stream`; all ranks must call it once per step. */
+/* One exchange step: store `local` into every rank's buffer (this rank's own included), then
+ * merge the `world` partials that land in this rank's buffer into `out`.  Two kernel launches
+ * on `stream`; all ranks must call it once per step. */
 PD_API int pd_exchange_step(const PdExchangeArgs* args);
 
 /* Decode and exchange in one: the streaming decode kernel stores every (request, kv head)
@@ -286,7 +285,7 @@ PD_API int pd_exchange_step(const PdExchangeArgs* args);
  * (PD_ERR_UNSUPPORTED when the streaming kernel does not serve it); its `out`, `result_f32` and
  * `result_lse` may all be NULL (the merged result goes to `exchange->out`).  `exchange->local`
  * is not used; rows, head_dim and rows_per_batch must match the decode
- * (rows = batch * num_q_heads) and rows_per_flag must be num_q_heads / num_kv_heads. */
+ * (rows = batch * num_q_heads). */
 PD_API int pd_decode_exchange(const PdDecodeArgs* decode, const PdExchangeArgs* exchange);
 
 /* Failure-path self-test with no counterpart in the reference: runs the kernels' bounded

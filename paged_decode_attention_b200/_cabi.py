@@ -86,7 +86,7 @@ class PdExchangeArgs(ctypes.Structure):
         ("local", _c_vp), ("rows", _c_i32), ("head_dim", _c_i32), ("rows_per_batch", _c_i32),
         ("out", _c_vp), ("out_stride_b", _c_i64), ("out_stride_h", _c_i64), ("io_dtype", _c_i32),
         ("result_f32", _c_vp), ("result_lse", _c_vp), ("status", _c_vp), ("stream", _c_vp),
-        ("rows_per_flag", _c_i32), ("phases", _c_i32), ("wait_limit_ns", _c_u64),
+        ("phases", _c_i32), ("wait_limit_ns", _c_u64),
     ]
 
 
@@ -145,9 +145,9 @@ def load() -> ctypes.CDLL:
     lib.pd_gather.restype = ctypes.c_int
     lib.pd_gather.argtypes = [ctypes.POINTER(PdGatherArgs)]
     lib.pd_exchange_bytes.restype = _c_u64
-    lib.pd_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32, _c_i32]
+    lib.pd_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32]
     lib.pd_exchange_part_offset.restype = _c_u64
-    lib.pd_exchange_part_offset.argtypes = [_c_i32] * 6
+    lib.pd_exchange_part_offset.argtypes = [_c_i32] * 5
     lib.pd_decode_exchange.restype = ctypes.c_int
     lib.pd_decode_exchange.argtypes = [ctypes.POINTER(PdDecodeArgs), ctypes.POINTER(PdExchangeArgs)]
     lib.pd_counter_bytes.restype = ctypes.c_int

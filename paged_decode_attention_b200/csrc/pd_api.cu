@@ -450,30 +450,22 @@ int pd_cache_write(const PdCacheWriteArgs* a) {
   return cudaGetLastError() == cudaSuccess ? PD_OK : PD_ERR_CUDA;
 }
 
-static int exchange_units(const PdExchangeArgs* a) {
-  const int per = a->rows_per_flag > 0 ? a->rows_per_flag : a->rows_per_batch;
-  return per > 0 && a->rows % per == 0 ? a->rows / per : -1;
+uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim) {
+  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0) return 0;
+  return exchange_bytes(world, rows, head_dim);
 }
 
-uint64_t pd_exchange_bytes(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag) {
-  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0 || rows_per_flag <= 0 || rows % rows_per_flag)
+uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t parity, int32_t rank) {
+  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0 || parity < 0 || parity > 1 || rank < 0 ||
+      rank >= world)
     return 0;
-  return exchange_bytes(world, (int64_t)rows * (head_dim + 1), rows / rows_per_flag);
-}
-
-uint64_t pd_exchange_part_offset(int32_t world, int32_t rows, int32_t head_dim, int32_t rows_per_flag,
-                                 int32_t parity, int32_t rank) {
-  if (world <= 0 || world > kMaxRanks || rows < 0 || head_dim <= 0 || rows_per_flag <= 0 || rows % rows_per_flag ||
-      parity < 0 || parity > 1 || rank < 0 || rank >= world)
-    return 0;
-  return exchange_part_offset(world, (int64_t)rows * (head_dim + 1), rows / rows_per_flag, parity, rank);
+  return exchange_part_offset(world, rows, head_dim, parity, rank);
 }
 
 static int check_exchange(const PdExchangeArgs* a, PeerPointers& peers) {
   if (!a || !a->peer_bufs) return PD_ERR_INVALID_ARG;
   if (a->world <= 0 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) return PD_ERR_INVALID_ARG;
   if (a->rows <= 0 || a->head_dim <= 0 || a->rows_per_batch <= 0) return PD_ERR_INVALID_ARG;
-  if (exchange_units(a) <= 0) return PD_ERR_INVALID_ARG;
   if (a->phases < 0 || a->phases > (PD_EXCHANGE_SEND | PD_EXCHANGE_MERGE)) return PD_ERR_INVALID_ARG;
   if (a->wait_limit_ns > kExchangeWaitNs) return PD_ERR_INVALID_ARG;
   const bool merging = a->phases == 0 || (a->phases & PD_EXCHANGE_MERGE);
@@ -496,7 +488,6 @@ static int launch_exchange_merge(const PdExchangeArgs* a, const PeerPointers& pe
   m.rows = a->rows;
   m.d = a->head_dim;
   m.rows_per_batch = a->rows_per_batch;
-  m.rows_per_flag = a->rows_per_flag > 0 ? a->rows_per_flag : a->rows_per_batch;
   m.out = a->out;
   m.dst_sb = a->out_stride_b;
   m.dst_sh = a->out_stride_h;
@@ -527,10 +518,9 @@ int pd_exchange_step(const PdExchangeArgs* a) {
   const bool merge = a->phases == 0 || (a->phases & PD_EXCHANGE_MERGE);
   if (send) {
     if (!a->local) return PD_ERR_INVALID_ARG;
-    if (!aligned(a->local, 16)) return PD_ERR_UNSUPPORTED;
-    const int64_t n = (int64_t)a->rows * (a->head_dim + 1);
-    exchange_push_kernel<<<a->world, 256, 0, (cudaStream_t)a->stream>>>(a->local, peers, a->world, a->rank, n,
-                                                                         exchange_units(a));
+    if (!aligned(a->local, 4)) return PD_ERR_INVALID_ARG;
+    exchange_push_kernel<<<a->world, 256, 0, (cudaStream_t)a->stream>>>(a->local, peers, a->world, a->rank, a->rows,
+                                                                         a->head_dim);
     if (cudaGetLastError() != cudaSuccess) return PD_ERR_CUDA;
   }
   return merge ? launch_exchange_merge(a, peers, false) : PD_OK;
@@ -545,7 +535,7 @@ int pd_decode_exchange(const PdDecodeArgs* d, const PdExchangeArgs* x) {
   if (d->kernel == PD_KERNEL_SIMPLE) return PD_ERR_UNSUPPORTED;
   if (d->num_q_heads % d->num_kv_heads) return PD_ERR_INVALID_ARG;
   if (x->rows != d->batch * d->num_q_heads || x->head_dim != d->head_dim || x->rows_per_batch != d->num_q_heads ||
-      x->rows_per_flag != d->num_q_heads / d->num_kv_heads || x->stream != d->stream)
+      x->stream != d->stream)
     return PD_ERR_INVALID_ARG;
   const int why = stream_supports(d);
   if (why != PD_OK) return why;
@@ -559,7 +549,6 @@ int pd_decode_exchange(const PdDecodeArgs* d, const PdExchangeArgs* x) {
     push.world = x->world;
     push.rank = x->rank;
     push.rows = x->rows;
-    push.units = d->batch * d->num_kv_heads;
     Params p;
     fill_params(d, p);
     const int drc = stream_run(d, p, sms, &push);

@@ -759,29 +759,21 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
     const float lse_out = denom > 0.f ? m + log2f(denom) : -INFINITY;
     if (p.res_o && c == 0) p.res_lse[(int64_t)b * p.hq + hq] = lse_out;
     if (push) {
-      // the same row into this rank's slot of every rank's exchange buffer (plain peer stores)
-      const int64_t n = (int64_t)push->rows * (D + 1);
+      // the same row into this rank's slot of every rank's exchange buffer: plain peer stores of
+      // marked words, which announce themselves (no fence, no flag)
       const int64_t grow = (int64_t)b * p.hq + hq;
       for (int r = 0; r < push->world; ++r) {
-        float* part = exchange_part(push->peers.buf[r], push->world, n, push->units, step & 1u, push->rank);
+        unsigned long long* part = exchange_part(push->peers.buf[r], push->world, push->rows, D, step & 1u, push->rank);
 #pragma unroll
-        for (int j = 0; j < J; ++j)
-          *reinterpret_cast<float4*>(part + grow * D + 16 * j + 4 * c) =
-              make_float4(acc[j][0] * inv, acc[j][1] * inv, acc[j][2] * inv, acc[j][3] * inv);
-        if (c == 0) part[(int64_t)push->rows * D + grow] = lse_out;
+        for (int j = 0; j < J; ++j) {
+          unsigned long long* at = part + grow * D + 16 * j + 4 * c;
+          store_marked2(at, acc[j][0] * inv, acc[j][1] * inv, step + 1u);
+          store_marked2(at + 2, acc[j][2] * inv, acc[j][3] * inv, step + 1u);
+        }
+        if (c == 0) store_marked(part + (int64_t)push->rows * D + grow, lse_out, step + 1u);
       }
     }
   }
-}
-
-// After a unit's rows went to every rank (merge_unit with push): make them visible system-wide,
-// then lane r raises the unit's flag in rank r's buffer.
-__device__ __forceinline__ void publish_unit(const PushTargets& push, uint32_t step, int unit, int lane) {
-  __threadfence_system();
-  __syncwarp();
-  if (lane < push.world)
-    store_release_sys(exchange_flag(push.peers.buf[lane], push.world, push.units, step & 1u, push.rank, unit),
-                      step + 1u);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -887,19 +879,14 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
       }
       if (pushing) {
         const uint32_t step = *push_step;
-        const int64_t n = (int64_t)sp.push.rows * (D + 1);
         for (int r = 0; r < sp.push.world; ++r) {
-          float* part = exchange_part(sp.push.peers.buf[r], sp.push.world, n, sp.push.units, step & 1u, sp.push.rank);
+          unsigned long long* part = exchange_part(sp.push.peers.buf[r], sp.push.world, sp.push.rows, D, step & 1u,
+                                                   sp.push.rank);
           for (int h = hb * HB * p.group; h < (hb + 1) * HB * p.group; ++h) {
-            for (int d = 0; d < D; ++d) part[((int64_t)b * p.hq + h) * D + d] = 0.f;
-            part[(int64_t)sp.push.rows * D + (int64_t)b * p.hq + h] = -INFINITY;
+            for (int d = 0; d < D; d += 2) store_marked2(part + ((int64_t)b * p.hq + h) * D + d, 0.f, 0.f, step + 1u);
+            store_marked(part + (int64_t)sp.push.rows * D + (int64_t)b * p.hq + h, -INFINITY, step + 1u);
           }
         }
-        __threadfence_system();
-        for (int r = 0; r < sp.push.world; ++r)
-          for (int kh = hb * HB; kh < (hb + 1) * HB; ++kh)
-            store_release_sys(exchange_flag(sp.push.peers.buf[r], sp.push.world, sp.push.units, step & 1u,
-                                            sp.push.rank, b * p.hkv + kh), step + 1u);
       }
     }
   }
@@ -1277,7 +1264,6 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
             __threadfence();
             merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
                               kMergeRadix, -1, pushing ? &sp.push : nullptr, *push_step);
-            if (pushing) publish_unit(sp.push, *push_step, vi.b * p.hkv + kvh, lane);
           }
         }
       } else {
@@ -1292,7 +1278,6 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
           __threadfence();
           merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane, 0, 0, 1, -1,
                             pushing ? &sp.push : nullptr, *push_step);
-          if (pushing) publish_unit(sp.push, *push_step, vi.b * p.hkv + kvh, lane);
         }
       }
     }

@@ -83,17 +83,17 @@ class PeerExchange:
 
     Every rank owns one exchange buffer in torch symmetric memory, mapped into all peers.  A
     step stores this rank's partial (fp32 results then lses) into every rank's buffer over
-    NVLink, raises flags there, and merges the partials that arrive in its own buffer.  Two
+    NVLink (every value as a word that carries the step's mark, so nothing is fenced or
+    flagged) and merges the partials that arrive in its own buffer.  Two
     forms: ``step()`` pushes a finished flat partial with a small kernel and merges
     (``pd_exchange_step``); ``fused_step(decode_args)`` lets the streaming decode kernel store
     each finished (request, kv head) unit itself and launches the merge behind it as a
     programmatic dependent (``pd_decode_exchange``).  Plain peer stores only — no multicast,
-    nothing is loaded from a peer's memory — and the wait for the flags is bounded
+    nothing is loaded from a peer's memory — and the wait for the words is bounded
     (``PD_DEV_TIMEOUT`` in ``status`` after one second).
     """
 
-    def __init__(self, local: torch.Tensor | None, out: torch.Tensor, group, status: torch.Tensor | None = None,
-                 rows_per_flag: int | None = None):
+    def __init__(self, local: torch.Tensor | None, out: torch.Tensor, group, status: torch.Tensor | None = None):
         import ctypes
         import os
 
@@ -110,10 +110,9 @@ class PeerExchange:
         if not out.is_contiguous():
             raise ValueError("out must be contiguous")
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        per_flag = hq if rows_per_flag is None else int(rows_per_flag)
-        nbytes = int(_cabi.load().pd_exchange_bytes(self.world, b * hq, d, per_flag))
+        nbytes = int(_cabi.load().pd_exchange_bytes(self.world, b * hq, d))
         if nbytes == 0:
-            raise ValueError("exchange supports at most 16 ranks and rows_per_flag must divide the rows")
+            raise ValueError("exchange supports at most 16 ranks")
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=out.device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group)
@@ -128,7 +127,7 @@ class PeerExchange:
         a.world, a.rank = self.world, self.rank
         if local is not None:
             a.local = local.data_ptr()
-        a.rows, a.head_dim, a.rows_per_batch, a.rows_per_flag = b * hq, d, hq, per_flag
+        a.rows, a.head_dim, a.rows_per_batch = b * hq, d, hq
         a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), hq * d, d
         a.io_dtype = _cabi.IO_CODE[out.dtype]
         if status is not None:
@@ -166,7 +165,7 @@ class KVRangeShardedDecoder:
     into ``out``.  ``exchange`` picks how the partials travel: ``"nccl"`` (one all-gather of the
     flat partial through the group's backend, then the merge kernel; the default, and the only
     one for CPU stand-ins over gloo), ``"peer"`` (a push kernel stores it into every rank's
-    buffer, a merge kernel waits for the flags), ``"fused"`` (the decode kernel stores each
+    buffer, a merge kernel waits for it), ``"fused"`` (the decode kernel stores each
     finished unit itself; the merge is launched behind it as a programmatic dependent).
     ``decode_fn``/``merge_fn`` default to the CUDA library; host-side tests inject CPU
     stand-ins to exercise the plumbing over gloo.
@@ -195,6 +194,7 @@ class KVRangeShardedDecoder:
         self.lses = self.gathered[:, self.n_o:].view(self.world, b, hq)
         self.out = torch.empty_like(q)
         self.graph = None
+        self.steps_per_replay = 1
         self._decode_step = None
         if decode_fn is None:
             from .decode import DecodeStep, MergeStep
@@ -209,9 +209,7 @@ class KVRangeShardedDecoder:
         self.launches_per_step = 2  # decode (merges its own splits), the cross-rank merge
         self.peer = None
         if exchange in ("peer", "fused") and dist.is_initialized():
-            group_size = hq // cache.shape.num_kv_heads
-            self.peer = PeerExchange(None if exchange == "fused" else self.local, self.out, group, status=status,
-                                     rows_per_flag=group_size if exchange == "fused" else None)
+            self.peer = PeerExchange(None if exchange == "fused" else self.local, self.out, group, status=status)
             self.launches_per_step = 2 if exchange == "fused" else 3  # decode, [push,] wait-and-merge
 
     def _run(self) -> None:
@@ -228,8 +226,13 @@ class KVRangeShardedDecoder:
             self.gathered[0].copy_(self.local)
         self.merge_fn(self.parts, self.lses, self.out)
 
-    def capture(self) -> None:
+    def capture(self, steps: int = 1) -> None:
         """Record the whole step into one CUDA graph; ``step`` then replays it.
+
+        ``steps`` > 1 records that many consecutive steps into the one graph (a serving engine's
+        graph holds a whole model step with one decode per layer; a measurement wants the device
+        time of a step without one graph launch per step); ``steps_per_replay`` says how many
+        steps a ``step()`` call then runs.
 
         At eight ranks a rank's slice of a long request decodes in a few tens of
         microseconds, less than the host needs to issue the operations; replaying a graph
@@ -243,8 +246,10 @@ class KVRangeShardedDecoder:
         torch.cuda.current_stream(self.q.device).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self._run()
+            for _ in range(max(1, int(steps))):
+                self._run()
         self.graph = graph
+        self.steps_per_replay = max(1, int(steps))
 
     def step(self) -> torch.Tensor:
         if self.graph is not None:
@@ -263,6 +268,7 @@ class KVRangeShardedDecoder:
         if self.q.is_cuda:
             torch.cuda.synchronize(self.q.device)
         graph, self.graph = self.graph, None
+        self.steps_per_replay = 1
         if graph is not None:
             graph.reset()
             del graph

@@ -177,22 +177,21 @@ def test_other_struct_layouts_match_header_field_order(struct):
     assert _header_fields(struct) == [f[0] for f in getattr(_cabi, struct)._fields_]
 
 
-@pytest.mark.parametrize("rows,d,per_flag", [(1, 64, 1), (6, 128, 3), (14, 64, 7), (14, 64, 14), (128, 128, 4),
-                                             (910, 1, 1)])
+@pytest.mark.parametrize("rows,d", [(1, 64), (6, 128), (14, 64), (128, 128), (910, 2), (3, 32)])
 @pytest.mark.parametrize("world", [1, 2, 3, 8, 16])
-def test_exchange_slots_are_16_byte_aligned_and_disjoint(world, rows, d, per_flag):
-    """A partial is rows * (d + 1) floats, odd-sized for most shapes; every (parity, rank) slot
-    must still start on a 16-byte boundary (the push copies with 16-byte stores), must not
-    overlap its neighbour and must end inside the buffer."""
+def test_exchange_slots_are_aligned_and_disjoint(world, rows, d):
+    """A partial is rows * (d + 1) words of 8 bytes, an odd count for odd row counts; every
+    (parity, rank) slot must still start on a 16-byte boundary (two words are stored at a time),
+    must not overlap its neighbour and must end inside the buffer."""
     lib = _cabi.load()
-    total = int(lib.pd_exchange_bytes(world, rows, d, per_flag))
-    assert total > 0 and total % 16 == 0
-    n_bytes = rows * (d + 1) * 4
+    total = int(lib.pd_exchange_bytes(world, rows, d))
+    assert total > 0 and total % 256 == 0
+    n_bytes = rows * (d + 1) * 8
     offs = []
     for parity in (0, 1):
         for r in range(world):
-            off = int(lib.pd_exchange_part_offset(world, rows, d, per_flag, parity, r))
-            assert off % 16 == 0 and off >= 256 + 2 * world * (rows // per_flag) * 4
+            off = int(lib.pd_exchange_part_offset(world, rows, d, parity, r))
+            assert off % 256 == 0 and off >= 256
             offs.append(off)
     assert offs == sorted(offs)
     for a, b in zip(offs, offs[1:]):
@@ -202,11 +201,10 @@ def test_exchange_slots_are_16_byte_aligned_and_disjoint(world, rows, d, per_fla
 
 def test_exchange_sizes_reject_bad_arguments():
     lib = _cabi.load()
-    assert lib.pd_exchange_bytes(17, 8, 64, 1) == 0       # more than 16 ranks
-    assert lib.pd_exchange_bytes(2, 9, 64, 2) == 0        # flags do not divide the rows
-    assert lib.pd_exchange_bytes(2, 8, 64, 0) == 0
-    assert lib.pd_exchange_part_offset(2, 8, 64, 1, 2, 0) == 0
-    assert lib.pd_exchange_part_offset(2, 8, 64, 1, 0, 2) == 0
+    assert lib.pd_exchange_bytes(17, 8, 64) == 0       # more than 16 ranks
+    assert lib.pd_exchange_bytes(2, 8, 0) == 0
+    assert lib.pd_exchange_part_offset(2, 8, 64, 2, 0) == 0
+    assert lib.pd_exchange_part_offset(2, 8, 64, 0, 2) == 0
     x = _cabi.PdExchangeArgs()
     assert lib.pd_exchange_step(ctypes.byref(x)) == -1
     assert lib.pd_decode_exchange(None, ctypes.byref(x)) == -1

@@ -482,3 +482,36 @@ def test_random_batches_match_the_oracle(seed):
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         helpers.assert_close(out, ref, bf16=case.io_dtype == "bf16", what=f"{case.name}/{kernel}/{splits}")
+
+
+def test_repeated_one_shot_calls_reuse_their_argument_block_and_follow_the_tensors(monkeypatch):
+    """paged_decode keeps the validated argument block of a call and reuses it when the next
+    call names the same tensors; anything that changes (a new lengths tensor, another out)
+    builds a new one, and data changed in place is simply read again by the kernel."""
+    case = cases.BY_NAME["llama8b_ragged"]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    built = []
+    real = pdec.build_args
+    monkeypatch.setattr(pdec, "build_args", lambda *a, **k: (built.append(1), real(*a, **k))[1])
+    monkeypatch.setattr(pdec, "_args_cache", {})
+    out = torch.empty_like(q)
+    first = pda.paged_decode(q, cache, out=out).clone()
+    again = pda.paged_decode(q, cache, out=out).clone()
+    assert len(built) == 1 and torch.equal(first, again)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    helpers.assert_close(again, ref, what="cached call")
+    # lengths halved IN PLACE: same argument block, the kernel reads the new values
+    cache.seq_lens.copy_(torch.clamp(cache.seq_lens // 2, min=1))
+    oc2 = dataclasses.replace(oc, seq_lens=np.maximum(oc.seq_lens // 2, 1).astype(np.int32))
+    half = pda.paged_decode(q, cache, out=out)
+    assert len(built) == 1
+    helpers.assert_close(half, c_oracle.decode(cases.q_as_f32(case, q_np), oc2), what="in-place lengths")
+    # a NEW lengths tensor: another address, another block
+    cache2 = dataclasses.replace(cache, seq_lens=torch.from_numpy(oc.seq_lens).cuda())
+    full = pda.paged_decode(q, cache2, out=out)
+    assert len(built) == 2
+    helpers.assert_close(full, ref, what="new lengths tensor")
+    pda.paged_decode(q, cache2)  # fresh out tensor each call: built again, still right
+    assert len(built) == 3

@@ -2,8 +2,8 @@
 
 Every rank's exchange buffer lives on the same device and every send is issued before any
 merge, so no kernel ever waits for a later launch; the merges find their flags set.  Covers
-the push kernel and the decode kernel's own push (pd_decode_exchange), partial sizes that are
-not a multiple of four floats, and the give-up path of the bounded wait.
+the push kernel and the decode kernel's own push (pd_decode_exchange), odd-sized partials, and
+the give-up path of the bounded wait.
 """
 
 from __future__ import annotations
@@ -26,9 +26,9 @@ pytestmark = pytest.mark.gpu
 class _Ranks:
     """`world` exchange buffers on one device and one PdExchangeArgs per played rank."""
 
-    def __init__(self, world, b, hq, d, per_flag, status=None, wait_ns=0):
+    def __init__(self, world, b, hq, d, status=None, wait_ns=0):
         lib = _cabi.load()
-        nbytes = int(lib.pd_exchange_bytes(world, b * hq, d, per_flag))
+        nbytes = int(lib.pd_exchange_bytes(world, b * hq, d))
         assert nbytes > 0
         self.bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
         self.ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in self.bufs])
@@ -38,7 +38,7 @@ class _Ranks:
             a = _cabi.PdExchangeArgs()
             a.peer_bufs = ctypes.cast(self.ptrs, ctypes.POINTER(ctypes.c_void_p))
             a.world, a.rank = world, r
-            a.rows, a.head_dim, a.rows_per_batch, a.rows_per_flag = b * hq, d, hq, per_flag
+            a.rows, a.head_dim, a.rows_per_batch = b * hq, d, hq
             a.out, a.out_stride_b, a.out_stride_h = self.outs[r].data_ptr(), hq * d, d
             a.io_dtype = 0
             a.wait_limit_ns = wait_ns
@@ -50,12 +50,13 @@ class _Ranks:
 
 @pytest.mark.parametrize("world,b,hq,d", [(2, 1, 14, 64), (3, 2, 6, 128), (8, 4, 32, 128), (2, 1, 1, 64)])
 def test_push_and_merge_with_every_rank_on_one_gpu(world, b, hq, d):
-    """n = rows * (d + 1) is not a multiple of four here (910, 1548, ..): every slot must still
-    take 16-byte stores, and the merge must equal the oracle's log-sum-exp merge."""
+    """Odd-sized partials (rows * (d + 1) = 910, 1548, .., 65 words): the two-word stores must
+    stay aligned, the odd last word must arrive too, and the merge must equal the oracle's
+    log-sum-exp merge."""
     lib = _cabi.load()
     gen = torch.Generator(device="cuda").manual_seed(world * 1000 + hq)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ranks = _Ranks(world, b, hq, d, hq, status=status)
+    ranks = _Ranks(world, b, hq, d, status=status)
     for step in range(3):  # both parities, and the step counter moving on
         locs = []
         for r in range(world):
@@ -92,9 +93,8 @@ def test_decode_kernel_pushes_its_own_units(name, batch, seq_len, world):
               for r in range(world)]
     q = shards[0][0]
     b, hq, d = q.shape
-    group = hq // shards[0][1].shape.num_kv_heads
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ranks = _Ranks(world, b, hq, d, group, status=status)
+    ranks = _Ranks(world, b, hq, d, status=status)
     steps = [pda.DecodeStep(q, cache, None, status=status, no_output=True) for _, cache in shards]
     for it in range(2):
         for r in range(world):
@@ -129,7 +129,7 @@ def test_merge_gives_up_when_a_rank_never_sends():
     lib = _cabi.load()
     b, hq, d = 2, 8, 64
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ranks = _Ranks(2, b, hq, d, hq, status=status, wait_ns=50_000_000)
+    ranks = _Ranks(2, b, hq, d, status=status, wait_ns=50_000_000)
     local = torch.randn(b * hq * (d + 1), device="cuda")
     ranks.args[0].local = local.data_ptr()
     assert lib.pd_exchange_step(ctypes.byref(ranks.args[0])) == 0
