@@ -40,13 +40,17 @@ import time
 
 ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# the exchange buffers of the KV-range-sharded block are written with plain peer stores only:
+# keep torch's symmetric memory from binding them to an NVLink multicast object (read when it
+# first allocates, so set before torch is imported)
+os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
 
 METRIC = "decode_attn_hbm_gbs"
 # DRAM bytes moved per algorithmic byte, from one ncu capture of the streaming kernel per
 # workload shape (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic KV bytes of
 # the captured case; see profiles/).  Traffic grows in proportion to the tokens processed, so
 # the ratio scales a full launch.
-NCU_TRAFFIC_RATIO = {"c2": 1.0136, "c3": 1.024, "c4": 1.015, "c5": 1.025}
+NCU_TRAFFIC_RATIO = {"c2": 1.013, "c3": 1.021, "c4": 1.013, "c5": 1.022}
 L2_BYTES = 126 << 20
 FALLBACK_HBM_GBS = 6650.0
 CPU_SUB_BATCH = 8  # requests per call of the CPU port: bounds its dense [b, Hkv, S_max, D] temporaries

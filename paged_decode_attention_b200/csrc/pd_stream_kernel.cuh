@@ -29,7 +29,9 @@
 // log-sum-exp into slot (worker + virtual sequence) of the scratch and takes a ticket on the
 // (request, kv head) counter; the warp whose ticket completes the count merges the request's
 // slots in place (pagedattn/triton_decode.py:221-240).  No second kernel, and no warp ever
-// waits for another.
+// waits for another.  Every counter is back at zero when the kernel ends.  In pushing mode
+// (KV-range sharding over several GPUs) every unit takes the merge path, and the merging warp
+// also stores the unit's rows into every rank's exchange buffer (pd_exchange_layout.cuh).
 //
 // Every wait is bounded: a wait that exceeds its limit sets PD_DEV_TIMEOUT in the status word,
 // raises the CTA's abort flag, and all warps leave their loops; the producer then waits (again
@@ -811,6 +813,12 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
   }
   // a cross-rank merge launched as a programmatic dependent may start now (a no-op otherwise)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the producer's first copies wait for the two tensor-map descriptors: fetch them now, while the
+  // CTA derives its share of the work
+  if (role == HB && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&tm_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&tm_v) : "memory");
+  }
   const bool pushing = sp.push.world > 0;
   volatile uint32_t* push_step = reinterpret_cast<volatile uint32_t*>(abort_flag + 2);
   if (tid == 0) {

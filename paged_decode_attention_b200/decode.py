@@ -220,7 +220,9 @@ _args_cache: dict[tuple, tuple] = {}
 def _call_key(q, cache, out, block_n, num_splits, sm_scale, kernel, result_f32, result_lse, status) -> tuple:
     """Everything an argument block is built from, as plain values (addresses, shapes, strides)."""
     k, v, bt, sl, ks, vs = cache.k_cache, cache.v_cache, cache.block_table, cache.seq_lens, cache.k_scale, cache.v_scale
-    return (q.data_ptr(), out.data_ptr(), k.data_ptr(), v.data_ptr(), bt.data_ptr(), sl.data_ptr(),
+    # the calling thread is part of the key: a cached block is refreshed in place (stream, scratch)
+    # on every call, so two threads must not share one
+    return (threading.get_ident(), q.data_ptr(), out.data_ptr(), k.data_ptr(), v.data_ptr(), bt.data_ptr(), sl.data_ptr(),
             q.shape, q.stride(), q.dtype, out.shape, out.stride(), out.dtype,
             k.shape, k.stride(), k.dtype, v.shape, v.stride(), v.dtype,
             bt.shape, bt.stride(), bt.dtype, sl.shape, sl.stride(), sl.dtype,
