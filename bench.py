@@ -405,7 +405,9 @@ def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:
         "us_per_call_cuda_graph": graph_us,
         "value": job_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
         "kv_bytes_job": job_bytes, "kv_bytes_rank0": my_bytes, "resident_pool_bytes_rank0": resident,
-        "l2": ("inputs fit in L2: latency-bound, microseconds only, no HBM claim" if l2_resident
+        "l2": ("inputs fit in L2: latency-bound, microseconds only, no HBM claim" if resident <= L2_BYTES
+               else f"inputs ({resident / 1e6:.0f} MB per GPU) are less than twice the {L2_BYTES >> 20} MB L2: "
+                    "part of a step may be served from it, no HBM fraction claimed" if l2_resident
                else f"inputs ({resident / 1e6:.0f} MB per GPU) exceed the {L2_BYTES >> 20} MB L2"),
         "roofline": None if l2_resident else {
             "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,

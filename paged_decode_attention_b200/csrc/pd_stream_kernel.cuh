@@ -690,38 +690,59 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
     const int row = r0 + q % rp;
     const bool live = row < p.group;
     const int64_t local = (int64_t)head_in_block * p.group + (live ? row : 0);
+    // One pass with a running maximum (the partials' data loads do not wait for a first pass
+    // over their log-sum-exps): when a partial raises the maximum, what has been summed so far is
+    // scaled down to it.  The phases are then brought to their common maximum and added.
     float m = -INFINITY;
-    for_ranges([&](int slot0, int n, int stride) {
-      const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
-#pragma unroll 4
-      for (int i = phase; i < n; i += sp_n) m = fmaxf(m, __ldcg(lp + (int64_t)i * stride * hg));
-    });
-    for (int sh = 4 * rp; sh < 32; sh <<= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, sh));
     float denom = 0.f;
     float acc[J][4];
 #pragma unroll
     for (int j = 0; j < J; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    if (m > -INFINITY) {
-      for_ranges([&](int slot0, int n, int stride) {
-        const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
-        const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
+    for_ranges([&](int slot0, int n, int stride) {
+      const float* lp = p.part_lse + (int64_t)slot0 * hg + local;
+      const float4* op = reinterpret_cast<const float4*>(p.part_o + ((int64_t)slot0 * hg + local) * D) + c;
 #pragma unroll(J > 8 ? 1 : 2)
-        for (int i = phase; i < n; i += sp_n) {
-          const float lse = __ldcg(lp + (int64_t)i * stride * hg);
-          float4 x[J];
+      for (int i = phase; i < n; i += sp_n) {
+        const float lse = __ldcg(lp + (int64_t)i * stride * hg);
+        float4 x[J];
 #pragma unroll
-          for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * stride * hg * (D / 4) + 4 * j);
-          const float wgt = lse > -INFINITY ? exp2f(lse - m) : 0.f;
-          denom += wgt;
+        for (int j = 0; j < J; ++j) x[j] = __ldcg(op + (int64_t)i * stride * hg * (D / 4) + 4 * j);
+        if (lse > m) {
+          const float down = m > -INFINITY ? exp2f(m - lse) : 0.f;
+          denom *= down;
 #pragma unroll
           for (int j = 0; j < J; ++j) {
-            acc[j][0] = fmaf(wgt, x[j].x, acc[j][0]);
-            acc[j][1] = fmaf(wgt, x[j].y, acc[j][1]);
-            acc[j][2] = fmaf(wgt, x[j].z, acc[j][2]);
-            acc[j][3] = fmaf(wgt, x[j].w, acc[j][3]);
+            acc[j][0] *= down;
+            acc[j][1] *= down;
+            acc[j][2] *= down;
+            acc[j][3] *= down;
           }
+          m = lse;
         }
-      });
+        const float wgt = lse > -INFINITY ? exp2f(lse - m) : 0.f;
+        denom += wgt;
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          acc[j][0] = fmaf(wgt, x[j].x, acc[j][0]);
+          acc[j][1] = fmaf(wgt, x[j].y, acc[j][1]);
+          acc[j][2] = fmaf(wgt, x[j].z, acc[j][2]);
+          acc[j][3] = fmaf(wgt, x[j].w, acc[j][3]);
+        }
+      }
+    });
+    if (sp_n > 1) {
+      float mall = m;
+      for (int sh = 4 * rp; sh < 32; sh <<= 1) mall = fmaxf(mall, __shfl_xor_sync(kFull, mall, sh));
+      const float down = m > -INFINITY ? exp2f(m - mall) : 0.f;  // mall is finite whenever m is
+      denom *= down;
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        acc[j][0] *= down;
+        acc[j][1] *= down;
+        acc[j][2] *= down;
+        acc[j][3] *= down;
+      }
+      m = mall;
     }
     for (int sh = 4 * rp; sh < 32; sh <<= 1) {
       denom += __shfl_xor_sync(kFull, denom, sh);

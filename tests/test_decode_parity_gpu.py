@@ -515,3 +515,42 @@ def test_repeated_one_shot_calls_reuse_their_argument_block_and_follow_the_tenso
     helpers.assert_close(full, ref, what="new lengths tensor")
     pda.paged_decode(q, cache2)  # fresh out tensor each call: built again, still right
     assert len(built) == 3
+
+
+@pytest.mark.parametrize("name", ["c2_mini", "c3_mini", "c5_mini", "c1_qwen05b"])
+def test_prepared_step_keeps_its_counters_at_zero_and_follows_new_addresses(name):
+    """DecodeStep vouches for its zero-filled scratch (PD_FLAG_COUNTERS_ZERO: no clear per call):
+    after every call the merge counters must be zero again, whatever the lengths were, and
+    step_at must serve fresh q / out / table / length buffers of the same layout."""
+    case = cases.BY_NAME[name]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    step = pda.DecodeStep(q, cache, status=status)
+    assert step.args.flags & _cabi.FLAG_COUNTERS_ZERO
+    n = ctypes.c_uint64(0)
+    _cabi.check(_cabi.load().pd_counter_bytes(ctypes.byref(step.args), ctypes.byref(n)), "pd_counter_bytes")
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    for _ in range(3):
+        out = step.step()
+        torch.cuda.synchronize()
+        helpers.assert_close(out, ref, bf16=case.io_dtype == "bf16", what="prepared step")
+        if n.value:
+            assert int(step._ws[: n.value].view(torch.int32).abs().sum()) == 0
+    # shorter lengths in place: other segment counts, same scratch
+    lens2 = np.maximum(oc.seq_lens // 3, 1).astype(np.int32)
+    cache.seq_lens.copy_(torch.from_numpy(lens2))
+    out = step.step()
+    ref2 = c_oracle.decode(cases.q_as_f32(case, q_np), dataclasses.replace(oc, seq_lens=lens2))
+    helpers.assert_close(out, ref2, bf16=case.io_dtype == "bf16", what="shorter lengths")
+    if n.value:
+        assert int(step._ws[: n.value].view(torch.int32).abs().sum()) == 0
+    # new buffers, same layout
+    q2, out2 = q.clone(), torch.empty_like(q)
+    bt2, sl2 = cache.block_table.clone(), torch.from_numpy(oc.seq_lens).cuda()
+    step.step_at(q2.data_ptr(), out2.data_ptr(), bt2.data_ptr(), sl2.data_ptr(),
+                 torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    helpers.assert_close(out2, ref, bf16=case.io_dtype == "bf16", what="step_at")
+    assert int(status.item()) == 0

@@ -48,3 +48,17 @@ def test_engine_captures_the_decode_path_into_its_cuda_graphs():
     device at replay) and the replays must give the stock backend's results."""
     res = _run_check("--cudagraph")
     assert res["cudagraph"] and res["stats"]["decode_calls"] > 0
+
+
+@pytest.mark.gpu
+def test_engine_with_the_flash_attention_parent():
+    """The variant that delegates prefill and mixed batches to the engine's FlashAttention
+    backend (cache laid out [2, NB, PAGE, H, D]): every pure-decode call still runs here and the
+    tokens match the stock FlashAttention backend's."""
+    if importlib.util.find_spec("vllm") is None or importlib.util.find_spec(
+            "vllm.v1.attention.backends.flash_attn") is None:
+        pytest.skip("the engine's FlashAttention backend is not installed")
+    res = _run_check("--parent", "flash")
+    assert res["timing"]["parent"] == "flash"
+    assert res["stats"]["decode_calls"] == res["expected_decode_calls"]
+    assert res["timing"]["delegated_attention_calls"] > 0
