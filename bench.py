@@ -386,7 +386,7 @@ def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:
     out = torch.empty_like(q)
     ns = args.num_splits if args.num_splits else None
     kernel_used = pdec.selected_kernel(pdec.build_args(q, cache, out, kernel=args.kernel, num_splits=ns))
-    prepared = pda.DecodeStep(q, cache, out, kernel=args.kernel, num_splits=ns)
+    prepared = pda.DecodeStep(q, cache, out, kernel=args.kernel, num_splits=ns, equal_tile_shares=args.equal_tile_shares)
     launches = 1 if (kernel_used == "stream" or pdec.workspace_bytes(prepared.args) == 0) else 2
     my_bytes = cache.bytes_read_per_decode_step()
     resident = sum(t.numel() * t.element_size() for t in (cache.k_cache, cache.v_cache))
@@ -615,6 +615,8 @@ def main() -> None:
     ap.add_argument("--exchange", choices=("fused", "peer", "nccl"), default="fused",
                     help="KV-range-sharded block: the decode kernel stores its units into the peers' buffers "
                          "(fused), a push kernel does (peer), or NCCL all-gather + merge (nccl)")
+    ap.add_argument("--equal-tile-shares", action="store_true",
+                    help="streaming kernel: equal tile counts per worker instead of equal estimated times (A/B)")
     ap.add_argument("--no-graph", action="store_true",
                     help="KV-range-sharded block: issue the step from the host instead of a CUDA graph")
     ap.add_argument("--pg-timeout", type=int, default=120, help="process-group timeout in seconds")

@@ -68,6 +68,11 @@ extern "C" {
                                     leaves its counters at zero).  The per-call clear of the
                                     counters, one memset node ahead of the kernel, is then skipped. */
 
+#define PD_FLAG_EQUAL_TILE_SHARES 2u /* streaming kernel: give every worker the same number of tiles
+                                       instead of shares of equal estimated time (a share that
+                                       crosses more request boundaries gets fewer tiles); for
+                                       A/B measurements */
+
 /* bits of the optional device status word (PdDecodeArgs.status) */
 #define PD_DEV_BAD_BLOCK 1u   /* a block-table entry was outside [0, num_blocks): page skipped */
 #define PD_DEV_TIMEOUT 2u     /* a bounded wait inside a kernel gave up                        */

@@ -101,6 +101,7 @@ EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
            "pd_exchange_step", "pd_exchange_part_offset", "pd_decode_exchange", "pd_counter_bytes")
 
 FLAG_COUNTERS_ZERO = 1
+FLAG_EQUAL_TILE_SHARES = 2
 EXCHANGE_SEND, EXCHANGE_MERGE = 1, 2
 
 STATIC_SCRATCH_BYTES = 8 << 20

@@ -35,9 +35,12 @@ static int head_block(int hkv) {
 }
 
 struct Shape {
-  int hb, nhb, wpc, splits, nvseq, stage_bytes;
+  int hb, nhb, wpc, splits, nvseq, stage_bytes, seg_cost;
   bool scaled;
 };
+
+// Workers (CTAs x workers per CTA) the cells' boundary table in shared memory is sized for.
+constexpr int kMaxWorkers = 1024;
 
 static Shape derive(const PdDecodeArgs* a) {
   Shape s;
@@ -56,17 +59,25 @@ static Shape derive(const PdDecodeArgs* a) {
   const int eb = is_16bit(a->kv_dtype) ? 2 : 1;
   // a tile of K (or V) is hb heads x 16 tokens x the row, whatever pieces the row is moved in
   s.stage_bytes = 2 * s.hb * kTileTokens * a->head_dim * eb + (s.scaled ? 2048 : 0);
+  // What one segment end costs a worker, in tiles' worth of its time: the shares of the tile line
+  // are balanced with it.  Per-CTA timelines put an end at 3-4 us and a tile at 1.5 us (16-bit
+  // pages) or 0.8 us (8-bit pages) of a worker's time, i.e. 2 and 5 tiles; swept on the full-size
+  // batches (0, 2, 4, 8, 12), the launches were shortest at 8 (ragged fp16: -1.2 %; uniform fp16:
+  // -0.6 % from 4 upwards) and at 12 (int8: -1.0 %) - an end also delays the worker's producer.
+  s.seg_cost = (a->flags & PD_FLAG_EQUAL_TILE_SHARES) ? 0 : (eb == 2 ? 8 : 12);
   return s;
 }
 
 struct SmemPlan {
   int nstage;
-  uint32_t bar_off, meta_off, misc_off, prefix_off, total;
+  uint32_t bar_off, meta_off, misc_off, prefix_off, count_off, bound_off, total;
 };
 
 static bool plan_smem(const Shape& s, SmemPlan& sm) {
   const uint32_t fixed_per_stage = (uint32_t)s.wpc * (16 + 4);
-  const uint32_t tail = 64 + (uint32_t)(s.nvseq + 2) * 4 + 1024 /* alignment slack */;
+  // lengths' prefix (int), count of non-empty sequences (u16), the cells' boundaries (int)
+  const uint32_t tail = 64 + (uint32_t)(s.nvseq + 2) * 6 + 16 + (uint32_t)(kMaxWorkers + 2) * 4 +
+                        1024 /* alignment slack */;
   int n = kMaxStages;
   for (; n >= 2; --n) {
     const uint64_t need = (uint64_t)n * s.wpc * s.stage_bytes + (uint64_t)n * fixed_per_stage + tail;
@@ -78,7 +89,9 @@ static bool plan_smem(const Shape& s, SmemPlan& sm) {
   sm.meta_off = sm.bar_off + (uint32_t)n * s.wpc * 16;
   sm.misc_off = (sm.meta_off + (uint32_t)n * s.wpc * 4 + 15u) & ~15u;
   sm.prefix_off = sm.misc_off + 16;
-  sm.total = sm.prefix_off + (uint32_t)(s.nvseq + 2) * 4 + 1024;
+  sm.count_off = sm.prefix_off + (uint32_t)(s.nvseq + 2) * 4;
+  sm.bound_off = (sm.count_off + (uint32_t)(s.nvseq + 2) * 2 + 15u) & ~15u;
+  sm.total = sm.bound_off + (uint32_t)(kMaxWorkers + 2) * 4 + 1024;
   return true;
 }
 
@@ -238,6 +251,9 @@ static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s,
   sp.meta_off = sm.meta_off;
   sp.misc_off = sm.misc_off;
   sp.prefix_off = sm.prefix_off;
+  sp.count_off = sm.count_off;
+  sp.bound_off = sm.bound_off;
+  sp.seg_cost = s.seg_cost;
   sp.tickets = (int32_t*)(scratch + wl.ticket_off);
   sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);
   if (push) sp.push = *push;
@@ -269,6 +285,7 @@ int stream_run(const PdDecodeArgs* a, Params& p, int sm_count, const PushTargets
   const Shape s = derive(a);
   SmemPlan sm;
   if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  if ((long long)sm_count * s.wpc > kMaxWorkers) return PD_ERR_UNSUPPORTED;
   const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
   if (!a->workspace || a->workspace_bytes < wl.total) return PD_ERR_WORKSPACE;
   CUtensorMap mk, mv;
@@ -309,6 +326,7 @@ static int stream_run_static(const PdDecodeArgs* a, Params& p, int sm_count) {
   const Shape s = derive(a);
   SmemPlan sm;
   if (!plan_smem(s, sm)) return PD_ERR_UNSUPPORTED;
+  if ((long long)sm_count * s.wpc > kMaxWorkers) return PD_ERR_UNSUPPORTED;
   const WorkspaceLayout wl = workspace_layout(a, s, sm_count);
   if (wl.total > (uint64_t)PD_STATIC_SCRATCH_BYTES) return PD_ERR_TOO_LARGE;
   char* scratch = (char*)static_scratch_address();

@@ -85,7 +85,8 @@ struct StreamCfg {
 struct StreamParams {
   Params p;
   int32_t nvseq, nhb, splits, nstage, wpc;
-  uint32_t bar_off, meta_off, misc_off, prefix_off;
+  uint32_t bar_off, meta_off, misc_off, prefix_off, count_off, bound_off;
+  int32_t seg_cost;  // tiles' worth of time that one segment end costs a worker (0: shares of equal tile counts)
   int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
   uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
   // KV-range-sharded runs: where every finished (request, kv head) unit is also stored, on every
@@ -640,14 +641,34 @@ __device__ __forceinline__ void consume_tile(
   }
 }
 
-// Segments (worker, virtual sequence) that cover request b / head block hb, in the order the
-// merge visits them: for every split with tiles, the workers first .. last of its tile range.
+// The tile line is cut into one cell per worker: cell w holds the tiles [bound[w], bound[w + 1]).
+// The cells are not equally long (a worker that crosses more request boundaries gets fewer
+// tiles, see the kernel), so the cell of a tile is found by bisection over the boundaries; every
+// thread derives the same boundaries from the lengths alone, which is what lets any warp count
+// and find the partial results of a request.
+struct CellMap {
+  const int* bound;  // workers + 1 non-decreasing tile indices, bound[0] = 0, bound[workers] = total
+  int workers;
+  // the cell that holds tile g (0 <= g < total): the last w with bound[w] <= g
+  __device__ __forceinline__ int of(int g) const {
+    int lo = 0, hi = workers;  // invariant: bound[lo] <= g < bound[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (bound[mid] <= g) lo = mid;
+      else hi = mid;
+    }
+    return lo;
+  }
+};
+
+// Segments (cell, virtual sequence) that cover request b / head block hb, in the order the
+// merge visits them: for every split with tiles, the cells first .. last of its tile range.
 template <typename F>
-__device__ __forceinline__ void for_each_segment(const int* prefix, int per, int v0, int splits, F&& f) {
+__device__ __forceinline__ void for_each_segment(const int* prefix, const CellMap& cm, int v0, int splits, F&& f) {
   for (int s = 0; s < splits; ++s) {
     const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
     if (last <= first) continue;
-    for (int wk = first / per; wk <= (last - 1) / per; ++wk) f(wk + v0 + s);
+    for (int c = cm.of(first); c <= cm.of(last - 1); ++c) f(c + v0 + s);
   }
 }
 
@@ -660,7 +681,7 @@ __device__ __forceinline__ void for_each_segment(const int* prefix, int per, int
 // lanes.  The per-phase sums are combined with shuffles.  Partials were written by other SMs:
 // they are read with ld.global.cg after the ticket's fence.
 template <int KV, int D>
-__device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, int per, int v0,
+__device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, const CellMap& cm, int v0,
                                            int splits, int hg, int head_in_block, int b, int kvh,
                                            int lane, int rslot0 = 0, int rn = 0, int rstride = 1,
                                            int dst_slot = -1, const PushTargets* push = nullptr,
@@ -676,7 +697,7 @@ __device__ __forceinline__ void merge_unit(const Params& p, const int* prefix, i
     for (int s = 0; s < splits; ++s) {
       const int first = prefix[v0 + s], last = prefix[v0 + s + 1];
       if (last <= first) continue;
-      f(first / per + v0 + s, (last - 1) / per - first / per + 1, 1);
+      f(cm.of(first) + v0 + s, cm.of(last - 1) - cm.of(first) + 1, 1);
     }
   };
   constexpr int J = D / 16;
@@ -814,6 +835,8 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw_addr);
   int* prefix = reinterpret_cast<int*>(smem + sp.prefix_off);
+  unsigned short* nonempty = reinterpret_cast<unsigned short*>(smem + sp.count_off);  // [v]: sequences before v that have tiles
+  int* bound = reinterpret_cast<int*>(smem + sp.bound_off);                            // the cells' boundaries
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + sp.misc_off);
 
   const Params& p = sp.p;
@@ -844,6 +867,7 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
   volatile uint32_t* push_step = reinterpret_cast<volatile uint32_t*>(abort_flag + 2);
   if (tid == 0) {
     prefix[0] = 0;
+    nonempty[0] = 0;
     *abort_flag = 0;
     // step counter of this rank's exchange buffer: its parity names the slots of this step
     *push_step = pushing ? *reinterpret_cast<volatile uint32_t*>(sp.push.peers.buf[sp.push.rank]) : 0u;
@@ -859,18 +883,27 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
   __syncthreads();
   volatile int* longest = abort_flag + 1;  // most tiles any virtual sequence has
   if (warp == 0) {
-    int carry = 0, most = 0;
+    int carry = 0, most = 0, ncarry = 0;
     for (int first = 1; first <= nv; first += 32) {
       const int idx = first + lane;
       int x = idx <= nv ? prefix[idx] : 0;
+      int c = x > 0 ? 1 : 0;  // virtual sequences with tiles, counted alongside
       most = max(most, x);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int y = __shfl_up_sync(kFull, x, o);
-        if (lane >= o) x += y;
+        const int z = __shfl_up_sync(kFull, c, o);
+        if (lane >= o) {
+          x += y;
+          c += z;
+        }
       }
-      if (idx <= nv) prefix[idx] = x + carry;
+      if (idx <= nv) {
+        prefix[idx] = x + carry;
+        nonempty[idx] = (unsigned short)(c + ncarry);
+      }
       carry += __shfl_sync(kFull, x, 31);
+      ncarry += __shfl_sync(kFull, c, 31);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(kFull, most, o));
@@ -880,12 +913,42 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
 
   const int total = prefix[nv];
   const int workers = gridDim.x * WPC;
-  int per = (total + workers - 1) / workers;
-  if (per < kMinTilesPerWorker) per = kMinTilesPerWorker;
   const int w = blockIdx.x * WPC + wl;  // global worker id
-  const long long g0l = (long long)w * per;
-  int g0 = g0l < total ? (int)g0l : total;
-  int g1 = g0 + per < total ? g0 + per : total;
+  // Shares of equal COST, not of equal tile counts.  The end of a segment - partial result,
+  // fence, ticket, perhaps a merge, the next request's query rows - costs a worker the time of
+  // seg_cost tiles during which it consumes nothing, and a worker whose share crosses many short
+  // requests pays it many times (per-CTA timelines of the ragged batch: 8 us at the median,
+  // 18 us at the worst, and the launch ends with the worst).  So every virtual sequence with
+  // tiles is charged its tiles plus seg_cost, the cost line is cut into equal parts, and each
+  // boundary is carried back to the tile line: into the sequence the cut falls in, or to its
+  // end when the cut falls into the surcharge.  A cut advances by more than seg_cost + 1, so no
+  // cell between two others is empty.  Everything is a function of the lengths: all CTAs
+  // derive the same boundaries, and two launches over the same lengths the same ones.
+  const int sc = sp.seg_cost;
+  const long long total_c = (long long)total + (long long)sc * nonempty[nv];
+  long long per_c = (total_c + workers - 1) / workers;
+  if (per_c < kMinTilesPerWorker + sc) per_c = kMinTilesPerWorker + sc;
+  for (int i = tid; i <= workers; i += kThreads) {
+    const long long c = (long long)i * per_c;
+    int tile = total;
+    if (c < total_c) {
+      int lo = 0, hi = nv;  // the last v whose cost prefix, prefix[v] + sc * nonempty[v], is <= c
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long)prefix[mid] + (long long)sc * nonempty[mid] <= c) lo = mid;
+        else hi = mid;
+      }
+      const int off = (int)(c - ((long long)prefix[lo] + (long long)sc * nonempty[lo]));
+      const int len = prefix[lo + 1] - prefix[lo];
+      tile = prefix[lo] + (off < len ? off : len);
+    }
+    bound[i] = tile;
+  }
+  __syncthreads();
+  CellMap cm;
+  cm.bound = bound;
+  cm.workers = workers;
+  int g0 = bound[w], g1 = bound[w + 1];
   // A small batch of short requests (fewer virtual sequences than workers, none longer than
   // kWholeTiles tiles) is dealt out whole, one request per worker, spread over the CTAs first:
   // every output row is then written directly, with no partial, ticket or merge on the way.
@@ -1265,8 +1328,8 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
       // request run on different SMs at the same time.
       int wfirst = 0, nseg = 0;
       if (sp.splits == 1) {
-        wfirst = prefix[v0] / per;
-        nseg = (prefix[v0 + 1] - 1) / per - wfirst + 1;
+        wfirst = cm.of(prefix[v0]);
+        nseg = cm.of(prefix[v0 + 1] - 1) - wfirst + 1;
       }
       if (nseg > kMergeRadix) {
         const int chunk = (w - wfirst) / kMergeRadix;
@@ -1281,7 +1344,7 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
         }
         if (__shfl_sync(kFull, done, 0)) {
           __threadfence();
-          merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, cslot, csize, 1, cslot);
+          merge_unit<KV, D>(p, prefix, cm, v0, 1, hg, role, vi.b, kvh, lane, cslot, csize, 1, cslot);
           __threadfence();
           __syncwarp();
           int last = 0;
@@ -1291,7 +1354,7 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
           }
           if (__shfl_sync(kFull, last, 0)) {
             __threadfence();
-            merge_unit<KV, D>(p, prefix, per, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
+            merge_unit<KV, D>(p, prefix, cm, v0, 1, hg, role, vi.b, kvh, lane, wfirst + v0, nchunk,
                               kMergeRadix, -1, pushing ? &sp.push : nullptr, *push_step);
           }
         }
@@ -1299,13 +1362,13 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
         int last = 0;
         if (lane == 0) {
           int expected = 0;
-          for_each_segment(prefix, per, v0, sp.splits, [&](int) { ++expected; });
+          for_each_segment(prefix, cm, v0, sp.splits, [&](int) { ++expected; });
           last = atomicAdd(unit_ticket, 1) + 1 == expected;
           if (last) *unit_ticket = 0;  // leave the counter as it was found
         }
         if (__shfl_sync(kFull, last, 0)) {
           __threadfence();
-          merge_unit<KV, D>(p, prefix, per, v0, sp.splits, hg, role, vi.b, kvh, lane, 0, 0, 1, -1,
+          merge_unit<KV, D>(p, prefix, cm, v0, sp.splits, hg, role, vi.b, kvh, lane, 0, 0, 1, -1,
                             pushing ? &sp.push : nullptr, *push_step);
         }
       }

@@ -85,11 +85,12 @@ def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *
                num_splits: int | None = None, sm_scale: float | None = None, kernel: str = "auto",
                result_f32: torch.Tensor | None = None, result_lse: torch.Tensor | None = None,
                status: torch.Tensor | None = None, max_seq_len: int = 0,
-               sm_count: int = 0, no_output: bool = False) -> _cabi.PdDecodeArgs:
+               sm_count: int = 0, no_output: bool = False, equal_tile_shares: bool = False) -> _cabi.PdDecodeArgs:
     """Validated argument block for ``pd_decode`` (no workspace attached yet).
 
     ``no_output`` leaves ``out`` unset: only ``pd_decode_exchange`` takes such a block (its
-    result leaves through the exchange buffers).
+    result leaves through the exchange buffers).  ``equal_tile_shares`` makes the streaming kernel
+    cut the work into equal tile counts instead of equal estimated times (for A/B measurements).
     """
     if q.dim() != 3:
         raise ValueError("q must be [batch, num_q_heads, head_dim]")
@@ -126,6 +127,8 @@ def build_args(q: torch.Tensor, cache: PagedKVCache, out: torch.Tensor | None, *
     args.kernel = _cabi.KERNEL_CODE[kernel]
     args.sm_count = int(sm_count)
     args.max_seq_len = int(max_seq_len)
+    if equal_tile_shares:
+        args.flags |= _cabi.FLAG_EQUAL_TILE_SHARES
     if (result_f32 is None) != (result_lse is None):
         raise ValueError("result_f32 and result_lse go together")
     if result_f32 is not None:
