@@ -339,7 +339,8 @@ __device__ __forceinline__ void consume_tile(
     const uint32_t (&kbase)[NT], const uint32_t (&scales)[NT], const int hkv, const int valid,
     const float scale_log2, const int lane,
     const uint32_t (&qb)[StreamCfg<KV, D, HB, SCALED>::KSTEPS][NG][2], const float (&qstep)[NG][2],
-    float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4]) {
+    float (&m)[NG][2], float (&l)[NG][2], float (&o)[StreamCfg<KV, D, HB, SCALED>::MT][NG][4],
+    float (&psum)[NG][4]) {
   using C = StreamCfg<KV, D, HB, SCALED>;
   constexpr unsigned kFull = 0xffffffffu;
   const int gq = lane >> 2, tq = lane & 3;
@@ -526,6 +527,15 @@ __device__ __forceinline__ void consume_tile(
         o[mt][ng][3] *= alpha[ng][1];
       }
     }
+    if constexpr (KV == PD_KV_I8) {
+#pragma unroll
+      for (int ng = 0; ng < NG; ++ng) {
+        psum[ng][0] *= alpha[ng][0];
+        psum[ng][1] *= alpha[ng][1];
+        psum[ng][2] *= alpha[ng][0];
+        psum[ng][3] *= alpha[ng][1];
+      }
+    }
   }
 
   // ---- O^T += V^T P^T ---------------------------------------------------------------------------
@@ -618,25 +628,15 @@ __device__ __forceinline__ void consume_tile(
     }
   }
   if constexpr (KV == PD_KV_I8) {
-    // Every int8 value entered as 1152 + x.  One more mma with an all-ones A gives, in every row,
-    // the sum over this call's tokens of P^T exactly as the tensor core read it; 1152 times that
-    // leaves each accumulator again before the call returns, so the running sums never carry
-    // the surplus from one call to the next.
-    float cs[NG][4];
+    // Every int8 value entered as 1152 + x.  One more mma with an all-ones A adds, in every row,
+    // the sum over this call's tokens of P^T exactly as the tensor core read it to the running
+    // column sums; they are rescaled with the accumulators, and 1152 times them leaves every
+    // accumulator once, when the segment ends (no multiply-add per accumulator and tile).
     const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-      cs[ng][0] = cs[ng][1] = cs[ng][2] = cs[ng][3] = 0.f;
 #pragma unroll
-      for (int u = 0; u < NT; ++u) mma_kv<KV>(cs[ng], ones, pb[u][ng][0], pb[u][ng][1]);
-    }
-#pragma unroll
-    for (int mt = 0; mt < C::MT; ++mt) {
-#pragma unroll
-      for (int ng = 0; ng < NG; ++ng) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) o[mt][ng][r] = fmaf(-1152.f, cs[ng][r], o[mt][ng][r]);
-      }
+      for (int u = 0; u < NT; ++u) mma_kv<KV>(psum[ng], ones, pb[u][ng][0], pb[u][ng][1]);
     }
   }
 }
@@ -1175,6 +1175,9 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
     for (int mt = 0; mt < C::MT; ++mt)
 #pragma unroll
       for (int ng = 0; ng < NG; ++ng) o[mt][ng][0] = o[mt][ng][1] = o[mt][ng][2] = o[mt][ng][3] = 0.f;
+    float psum[NG][4];  // int8 pages: running column sums of P^T (see consume_tile)
+#pragma unroll
+    for (int ng = 0; ng < NG; ++ng) psum[ng][0] = psum[ng][1] = psum[ng][2] = psum[ng][3] = 0.f;
 
     // 8-bit tiles with a deep ring (five stages or more) are taken two at a time: one softmax
     // step per 32 tokens and two independent score chains per warp.  With fewer stages the
@@ -1204,10 +1207,10 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
             const int remaining1 = remaining - kTileTokens;  // >= 1: the next tile is of this request
             if (remaining1 >= kTileTokens)
               consume_tile<KV, D, HB, SCALED, NG, false, 2>(kb, sc, p.hkv, kTileTokens, p.scale_log2,
-                                                            lane, qb, qstep, m, l, o);
+                                                            lane, qb, qstep, m, l, o, psum);
             else
               consume_tile<KV, D, HB, SCALED, NG, true, 2>(kb, sc, p.hkv, remaining1, p.scale_log2,
-                                                           lane, qb, qstep, m, l, o);
+                                                           lane, qb, qstep, m, l, o, psum);
             __syncwarp();
             if (lane == 0) {
               mbar_arrive(empty0 + 8 * st);
@@ -1226,10 +1229,10 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
         const uint32_t sc[1] = {sbase + 2 * C::TILE_BYTES + kvh * 2};
         if (remaining >= kTileTokens)
           consume_tile<KV, D, HB, SCALED, NG, false>(kb, sc, p.hkv, kTileTokens, p.scale_log2,
-                                                     lane, qb, qstep, m, l, o);
+                                                     lane, qb, qstep, m, l, o, psum);
         else
           consume_tile<KV, D, HB, SCALED, NG, true>(kb, sc, p.hkv, remaining, p.scale_log2,
-                                                    lane, qb, qstep, m, l, o);
+                                                    lane, qb, qstep, m, l, o, psum);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * st);
@@ -1240,6 +1243,17 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
     if (aborted) break;
 
     // ---- segment epilogue: the thread owns heads 2t, 2t+1 (+8 per n-tile) -----------------------
+    if constexpr (KV == PD_KV_I8) {
+      // the surplus of the biased int8 values: 1152 times the column sums of P^T, rows alike
+#pragma unroll
+      for (int mt = 0; mt < C::MT; ++mt) {
+#pragma unroll
+        for (int ng = 0; ng < NG; ++ng) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) o[mt][ng][r] = fmaf(-1152.f, psum[ng][r], o[mt][ng][r]);
+        }
+      }
+    }
     const float unscale = SCALED ? (1.f / 256.f) : 1.f;
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
