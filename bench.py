@@ -355,8 +355,9 @@ def e2e_steps(env: Env, cache, q, kernel: str, steps: int, job_bytes: float) -> 
     e2e_step = env.reduce([time.perf_counter() - t0], "max")[0] / steps
     return {"value": job_bytes / e2e_step / 1e9, "unit": "GB/s", "us_per_call": e2e_step * 1e6,
             "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes,
-            "note": "pd_decode_host: q, block table and lengths from pinned host memory, result "
-                    "copied back; the KV pages are device state and stay in HBM"}
+            "note": "pd_decode_host: q, block table and lengths copied from pinned host memory, the result "
+                    "rows written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT); the "
+                    "KV pages are device state and stay in HBM"}
 
 
 def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:

@@ -73,6 +73,18 @@ extern "C" {
                                        crosses more request boundaries gets fewer tiles); for
                                        A/B measurements */
 
+#define PD_FLAG_HOST_DIRECT_OUT 4u /* pd_decode_host only: out_host is page-locked host memory the device
+                                      can address (cudaHostAlloc, cudaHostRegister; what torch's
+                                      pin_memory() gives).  The kernels then write the result rows there
+                                      themselves, across the bus and while the KV pages stream, instead
+                                      of the result being staged in args->out and copied back behind the
+                                      kernel.  A pointer the device cannot address is staged as without
+                                      the flag. */
+#define PD_FLAG_HOST_DIRECT_Q 8u   /* the same for q_host: the kernels read the query rows from host
+                                      memory.  Pays only for small batches: a worker waits for its
+                                      query rows when a request starts, and across the bus that wait is
+                                      several times longer. */
+
 /* bits of the optional device status word (PdDecodeArgs.status) */
 #define PD_DEV_BAD_BLOCK 1u   /* a block-table entry was outside [0, num_blocks): page skipped */
 #define PD_DEV_TIMEOUT 2u     /* a bounded wait inside a kernel gave up                        */
@@ -204,9 +216,10 @@ PD_API int pd_decode(const PdDecodeArgs* args);
 
 /* The same step for callers that hold q, block_table, seq_lens and out in HOST memory:
  * copies the three inputs into the device buffers named by `args` (which must be large
- * enough), runs pd_decode, copies `out` back and waits for the stream.  The KV pages stay
- * where they live, on the device.  No counterpart in the reference, whose callers pass
- * CUDA tensors. */
+ * enough), runs pd_decode, copies `out` back and waits for the stream.  With
+ * PD_FLAG_HOST_DIRECT_OUT / PD_FLAG_HOST_DIRECT_Q in args->flags the kernels use the caller's
+ * page-locked out_host / q_host in place instead of that copy.  The KV pages stay where they
+ * live, on the device.  No counterpart in the reference, whose callers pass CUDA tensors. */
 PD_API int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
 
 /* Bytes of workspace pd_decode needs for these arguments (depends on sizes, dtype, kernel

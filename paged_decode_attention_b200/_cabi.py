@@ -102,6 +102,8 @@ EXPORTS = ("pd_abi_version", "pd_status_string", "pd_decode", "pd_decode_host",
 
 FLAG_COUNTERS_ZERO = 1
 FLAG_EQUAL_TILE_SHARES = 2
+FLAG_HOST_DIRECT_OUT = 4
+FLAG_HOST_DIRECT_Q = 8
 EXCHANGE_SEND, EXCHANGE_MERGE = 1, 2
 
 STATIC_SCRATCH_BYTES = 8 << 20

@@ -27,6 +27,17 @@ static int cached_sm_count() {
 
 static bool aligned(const void* p, uintptr_t a) { return ((uintptr_t)p % a) == 0; }
 
+// The address under which the current device reaches page-locked host memory at `host`, or
+// nullptr when `host` is ordinary (pageable) memory or memory of another kind.
+static void* device_view_of_host(const void* host) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 static int elem_bytes(int kv) { return (kv == PD_KV_F16 || kv == PD_KV_BF16) ? 2 : 1; }
 
 // Checks everything that can be checked without touching the device.
@@ -306,8 +317,28 @@ int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io) {
     return PD_ERR_INVALID_ARG;
   const cudaStream_t st = (cudaStream_t)args->stream;
   const size_t qo = (size_t)args->batch * args->num_q_heads * args->head_dim * 2;
+  // PD_FLAG_HOST_DIRECT_*: where the device can address the caller's result (or query) buffer,
+  // the kernels use it in place, and the copy behind (or ahead of) the kernel becomes traffic
+  // that overlaps the KV stream.
+  PdDecodeArgs a = *args;
+  a.flags &= ~(PD_FLAG_HOST_DIRECT_OUT | PD_FLAG_HOST_DIRECT_Q);
+  bool q_direct = false, out_direct = false;
+  if (args->flags & PD_FLAG_HOST_DIRECT_Q) {
+    void* dq = device_view_of_host(io->q_host);
+    if (dq && ((uintptr_t)dq % 16) == 0) {
+      a.q = dq;
+      q_direct = true;
+    }
+  }
+  if (args->flags & PD_FLAG_HOST_DIRECT_OUT) {
+    void* dout = device_view_of_host(io->out_host);
+    if (dout && ((uintptr_t)dout % 16) == 0) {
+      a.out = dout;
+      out_direct = true;
+    }
+  }
   if (args->batch > 0) {
-    if (cudaMemcpyAsync((void*)args->q, io->q_host, qo, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+    if ((!q_direct && cudaMemcpyAsync((void*)args->q, io->q_host, qo, cudaMemcpyHostToDevice, st) != cudaSuccess) ||
         cudaMemcpyAsync((void*)args->block_table, io->block_table_host,
                         (size_t)args->batch * args->max_blocks_per_seq * 4, cudaMemcpyHostToDevice,
                         st) != cudaSuccess ||
@@ -315,9 +346,9 @@ int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io) {
                         cudaMemcpyHostToDevice, st) != cudaSuccess)
       return PD_ERR_CUDA;
   }
-  const int drc = pd_decode(args);
+  const int drc = pd_decode(&a);
   if (drc != PD_OK) return drc;
-  if (args->batch > 0 &&
+  if (args->batch > 0 && !out_direct &&
       cudaMemcpyAsync(io->out_host, args->out, qo, cudaMemcpyDeviceToHost, st) != cudaSuccess)
     return PD_ERR_CUDA;
   return cudaStreamSynchronize(st) == cudaSuccess ? PD_OK : PD_ERR_CUDA;

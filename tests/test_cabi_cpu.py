@@ -41,6 +41,25 @@ def test_struct_layout_matches_header_field_order():
     assert names == [f[0] for f in _cabi.PdDecodeArgs._fields_]
 
 
+def test_flag_and_size_constants_match_the_header():
+    """The Python side's copies of the header's #defines."""
+    import re
+    text = (ROOT / "include" / "paged_decode.h").read_text()
+    defines = {m.group(1): m.group(2) for m in re.finditer(r"#define\s+(PD_\w+)\s+\(?([-\w<> ]+?)\)?\s*(?:/\*|$)", text, re.M)}
+
+    def value(name):
+        return eval(defines[name].replace("u", ""))  # noqa: S307 - literals of the header
+
+    assert value("PD_ABI_VERSION") == _cabi.ABI_VERSION
+    for name in ("COUNTERS_ZERO", "EQUAL_TILE_SHARES", "HOST_DIRECT_OUT", "HOST_DIRECT_Q"):
+        assert value(f"PD_FLAG_{name}") == getattr(_cabi, f"FLAG_{name}"), name
+    flags = [value(f"PD_FLAG_{n}") for n in ("COUNTERS_ZERO", "EQUAL_TILE_SHARES", "HOST_DIRECT_OUT", "HOST_DIRECT_Q")]
+    assert sorted(flags) == [1, 2, 4, 8]
+    assert value("PD_STATIC_SCRATCH_BYTES") == _cabi.STATIC_SCRATCH_BYTES
+    assert (value("PD_EXCHANGE_SEND"), value("PD_EXCHANGE_MERGE")) == (_cabi.EXCHANGE_SEND, _cabi.EXCHANGE_MERGE)
+    assert (value("PD_DEV_BAD_BLOCK"), value("PD_DEV_TIMEOUT")) == (_cabi.DEV_BAD_BLOCK, _cabi.DEV_TIMEOUT)
+
+
 def test_status_strings():
     assert _cabi.status_string(0) == "ok"
     for rc in (-1, -2, -3, -4):

@@ -344,6 +344,32 @@ def test_host_buffer_entry_point_equals_device_call(golden):
     helpers.assert_close(out_host, golden[f"{case.name}/out_f32"], what="host entry")
 
 
+@pytest.mark.parametrize("name", ["c1_qwen05b", "llama8b_ragged", "llama8b_int8_s2048", "c4_mini"])
+@pytest.mark.parametrize("direct", ["out", "q", "both"])
+def test_host_buffers_used_in_place_give_the_staged_result(name, direct):
+    """PD_FLAG_HOST_DIRECT_OUT / _Q: the kernels write the result to, and read q from, the caller's
+    pinned buffers themselves.  Same bits as the staged call; pageable buffers fall back to staging."""
+    case = cases.BY_NAME[name]
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    q_t = torch.from_numpy(q_np) if case.io_dtype != "bf16" else torch.from_numpy(q_np).view(torch.bfloat16)
+    bt, sl = torch.from_numpy(oc.block_table), torch.from_numpy(oc.seq_lens)
+
+    def run(mode, pinned=True):
+        dec = pda.HostDecoder(cache, io_dtype=q_t.dtype, direct=mode)
+        out = torch.full(q_t.shape, 7.0, dtype=q_t.dtype)
+        pin = (lambda t: t.pin_memory()) if pinned else (lambda t: t.clone())
+        out = pin(out)
+        dec.step(pin(q_t), pin(bt), pin(sl), out)
+        return out
+
+    staged = run("none")
+    helpers.assert_close(staged, ref, bf16=case.io_dtype == "bf16", what=f"{name} staged")
+    assert torch.equal(run(direct), staged), "in-place host buffers must give the staged bits"
+    assert torch.equal(run(direct, pinned=False), staged), "pageable buffers are staged as before"
+
+
 def test_rejects_bad_arguments_without_launching():
     case = cases.BY_NAME["llama8b_b2_s64"]
     q_np, oc = cases.build(case)
