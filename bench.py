@@ -340,13 +340,17 @@ def e2e_steps(env: Env, cache, q, kernel: str, steps: int, job_bytes: float) -> 
     import paged_decode_attention_b200 as pda
 
     torch = env.torch
-    host = pda.HostDecoder(cache, kernel=kernel)
+    host = pda.HostDecoder(cache, kernel=kernel, direct=env.args.e2e_direct)
     q_h = q.cpu().pin_memory()
     bt_h = cache.block_table.cpu().pin_memory()
     sl_h = cache.seq_lens.cpu().pin_memory()
     out_h = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-    for _ in range(3):
+    # Warm-up by time as well as by count: pinning the host copies above leaves the GPU idle for
+    # milliseconds, and the first steps after that run while its clocks are still coming back up.
+    warm_until, n = time.perf_counter() + 0.05, 0
+    while n < max(3, env.args.warmup) or time.perf_counter() < warm_until:
         host.step(q_h, bt_h, sl_h, out_h)
+        n += 1
     env.sync_all()
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -356,8 +360,8 @@ def e2e_steps(env: Env, cache, q, kernel: str, steps: int, job_bytes: float) -> 
     return {"value": job_bytes / e2e_step / 1e9, "unit": "GB/s", "us_per_call": e2e_step * 1e6,
             "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes,
             "note": "pd_decode_host: q, block table and lengths copied from pinned host memory, the result "
-                    "rows written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT); the "
-                    "KV pages are device state and stay in HBM"}
+                    f"rows {'written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT)' if env.args.e2e_direct in ('out', 'both') else 'copied back'}; "
+                    "the KV pages are device state and stay in HBM", "direct": env.args.e2e_direct}
 
 
 def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:
@@ -618,6 +622,9 @@ def main() -> None:
                          "(fused), a push kernel does (peer), or NCCL all-gather + merge (nccl)")
     ap.add_argument("--equal-tile-shares", action="store_true",
                     help="streaming kernel: equal tile counts per worker instead of equal estimated times (A/B)")
+    ap.add_argument("--e2e-direct", choices=("out", "none", "q", "both"), default="out",
+                    help="e2e: which pinned host buffers the kernels use in place instead of a staging copy "
+                         "(PD_FLAG_HOST_DIRECT_OUT / _Q); none = every buffer staged (A/B)")
     ap.add_argument("--no-graph", action="store_true",
                     help="KV-range-sharded block: issue the step from the host instead of a CUDA graph")
     ap.add_argument("--pg-timeout", type=int, default=120, help="process-group timeout in seconds")
