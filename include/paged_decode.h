@@ -80,6 +80,9 @@ extern "C" {
                                       of the result being staged in args->out and copied back behind the
                                       kernel.  A pointer the device cannot address is staged as without
                                       the flag. */
+#define PD_FLAG_HOST_DIRECT_BT 16u  /* the same for block_table_host: the kernels fetch the entries they
+                                      need (one 128-byte read per 32 tiles of a worker) across the bus
+                                      instead of the whole padded table being copied ahead of them */
 #define PD_FLAG_HOST_DIRECT_Q 8u   /* the same for q_host: the kernels read the query rows from host
                                       memory.  Pays only for small batches: a worker waits for its
                                       query rows when a request starts, and across the bus that wait is
@@ -217,8 +220,8 @@ PD_API int pd_decode(const PdDecodeArgs* args);
 /* The same step for callers that hold q, block_table, seq_lens and out in HOST memory:
  * copies the three inputs into the device buffers named by `args` (which must be large
  * enough), runs pd_decode, copies `out` back and waits for the stream.  With
- * PD_FLAG_HOST_DIRECT_OUT / PD_FLAG_HOST_DIRECT_Q in args->flags the kernels use the caller's
- * page-locked out_host / q_host in place instead of that copy.  The KV pages stay where they
+ * PD_FLAG_HOST_DIRECT_OUT / _BT / _Q in args->flags the kernels use the caller's page-locked
+ * out_host / block_table_host / q_host in place instead of that copy.  The KV pages stay where they
  * live, on the device.  No counterpart in the reference, whose callers pass CUDA tensors. */
 PD_API int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io);
 

@@ -321,8 +321,15 @@ int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io) {
   // the kernels use it in place, and the copy behind (or ahead of) the kernel becomes traffic
   // that overlaps the KV stream.
   PdDecodeArgs a = *args;
-  a.flags &= ~(PD_FLAG_HOST_DIRECT_OUT | PD_FLAG_HOST_DIRECT_Q);
-  bool q_direct = false, out_direct = false;
+  a.flags &= ~(PD_FLAG_HOST_DIRECT_OUT | PD_FLAG_HOST_DIRECT_Q | PD_FLAG_HOST_DIRECT_BT);
+  bool q_direct = false, out_direct = false, bt_direct = false;
+  if (args->flags & PD_FLAG_HOST_DIRECT_BT) {
+    void* dbt = device_view_of_host(io->block_table_host);
+    if (dbt && ((uintptr_t)dbt % 4) == 0) {
+      a.block_table = (const int32_t*)dbt;
+      bt_direct = true;
+    }
+  }
   if (args->flags & PD_FLAG_HOST_DIRECT_Q) {
     void* dq = device_view_of_host(io->q_host);
     if (dq && ((uintptr_t)dq % 16) == 0) {
@@ -339,9 +346,9 @@ int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io) {
   }
   if (args->batch > 0) {
     if ((!q_direct && cudaMemcpyAsync((void*)args->q, io->q_host, qo, cudaMemcpyHostToDevice, st) != cudaSuccess) ||
-        cudaMemcpyAsync((void*)args->block_table, io->block_table_host,
-                        (size_t)args->batch * args->max_blocks_per_seq * 4, cudaMemcpyHostToDevice,
-                        st) != cudaSuccess ||
+        (!bt_direct && cudaMemcpyAsync((void*)args->block_table, io->block_table_host,
+                                       (size_t)args->batch * args->max_blocks_per_seq * 4, cudaMemcpyHostToDevice,
+                                       st) != cudaSuccess) ||
         cudaMemcpyAsync((void*)args->seq_lens, io->seq_lens_host, (size_t)args->batch * 4,
                         cudaMemcpyHostToDevice, st) != cudaSuccess)
       return PD_ERR_CUDA;

@@ -405,16 +405,18 @@ class HostDecoder:
     Owns device staging buffers for the per-step inputs and the output; the KV pages are
     device state and stay on the GPU.  ``step`` goes through ``pd_decode_host``: three
     host-to-device copies, the decode, the result back, one stream wait.  ``direct`` names the
-    caller's pinned buffers the kernels use in place instead of a staging copy: ``"out"`` (the
-    default: result rows are written across the bus as they are finished, while the KV pages
-    still stream - 3 to 13 % off a step of the five bench workloads), ``"q"``, ``"both"`` (the
-    query rows read across the bus too: pays only for small batches such as the 24-request c1,
-    a worker waits for them at every request start) or ``"none"``.  Pageable host tensors are
-    always staged.
+    caller's pinned buffers the kernels use in place instead of a staging copy, joined by "+":
+    ``"out"`` (result rows are written across the bus as they are finished, while the KV pages
+    still stream: 3 to 13 % off a step of the five bench workloads), ``"bt"`` (the producers
+    fetch the block-table entries they need across the bus instead of the whole padded table
+    being copied first: up to 5 % more), ``"q"`` (the query rows read across the bus too: pays
+    only for small batches such as the 24-request c1, a worker waits for them at every request
+    start; ``"both"`` = ``"out+q"``) or ``"none"``.  Default ``"out+bt"``.  Pageable host
+    tensors are always staged.
     """
 
     def __init__(self, cache: PagedKVCache, io_dtype: torch.dtype = torch.float16,
-                 sm_scale: float | None = None, kernel: str = "auto", direct: str = "out"):
+                 sm_scale: float | None = None, kernel: str = "auto", direct: str = "out+bt"):
         dev = cache.k_cache.device
         b, hq, d = cache.batch, cache.shape.num_q_heads, cache.shape.head_dim
         self.q_dev = torch.empty((b, hq, d), dtype=io_dtype, device=dev)
@@ -423,8 +425,10 @@ class HostDecoder:
         self.args = build_args(self.q_dev, cache, self.out_dev, sm_scale=sm_scale, kernel=kernel)
         # `direct`: which of the caller's pinned buffers the kernels use in place instead of the
         # staging buffers q_dev / out_dev (PD_FLAG_HOST_DIRECT_OUT, PD_FLAG_HOST_DIRECT_Q)
-        self.args.flags |= {"none": 0, "out": _cabi.FLAG_HOST_DIRECT_OUT, "q": _cabi.FLAG_HOST_DIRECT_Q,
-                            "both": _cabi.FLAG_HOST_DIRECT_OUT | _cabi.FLAG_HOST_DIRECT_Q}[direct]
+        bits = {"out": _cabi.FLAG_HOST_DIRECT_OUT, "q": _cabi.FLAG_HOST_DIRECT_Q, "bt": _cabi.FLAG_HOST_DIRECT_BT,
+                "none": 0, "both": _cabi.FLAG_HOST_DIRECT_OUT | _cabi.FLAG_HOST_DIRECT_Q}
+        for part in direct.split("+"):
+            self.args.flags |= bits[part]
         need = ctypes.c_uint64(0)
         _cabi.check(_call_on_device(dev, _cabi.load().pd_workspace_bytes, ctypes.byref(self.args),
                                     ctypes.byref(need)), "pd_workspace_bytes")

@@ -345,10 +345,10 @@ def test_host_buffer_entry_point_equals_device_call(golden):
 
 
 @pytest.mark.parametrize("name", ["c1_qwen05b", "llama8b_ragged", "llama8b_int8_s2048", "c4_mini"])
-@pytest.mark.parametrize("direct", ["out", "q", "both"])
+@pytest.mark.parametrize("direct", ["out", "bt", "q", "out+bt+q"])
 def test_host_buffers_used_in_place_give_the_staged_result(name, direct):
-    """PD_FLAG_HOST_DIRECT_OUT / _Q: the kernels write the result to, and read q from, the caller's
-    pinned buffers themselves.  Same bits as the staged call; pageable buffers fall back to staging."""
+    """PD_FLAG_HOST_DIRECT_OUT / _BT / _Q: the kernels write the result to, and read the block table
+    and q from, the caller's pinned buffers themselves.  Same bits as the staged call; pageable buffers fall back to staging."""
     case = cases.BY_NAME[name]
     q_np, oc = cases.build(case)
     cache = helpers.to_device_cache(oc)
