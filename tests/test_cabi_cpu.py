@@ -112,6 +112,26 @@ def test_kernel_selection_by_row_width(kv_dtype, d, expect):
     assert _cabi.load().pd_select_kernel(ctypes.byref(args)) == expect
 
 
+def test_kernel_selection_at_the_virtual_sequence_limit():
+    """The streaming kernel lays out at most 4096 virtual sequences (requests x head blocks x
+    explicit splits); one more and the request goes to the general kernel, or is refused when the
+    streaming kernel was asked for by name."""
+    lib = _cabi.load()
+    q, cache = _cpu_case(hq=32, hkv=8, d=128, b=2, s=40)
+    args = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    for batch, splits, expect in ((4096, 1, 2), (4097, 1, 1), (512, 8, 2), (513, 8, 1), (1, 1024, 2)):
+        args.batch, args.num_splits, args.kernel = batch, splits, 0
+        assert lib.pd_select_kernel(ctypes.byref(args)) == expect, (batch, splits)
+    args.batch, args.num_splits, args.kernel = 4097, 1, 2
+    assert lib.pd_select_kernel(ctypes.byref(args)) == -2
+    # 16 kv heads are two head blocks of eight: half as many requests fit
+    q, cache = _cpu_case(hq=32, hkv=16, d=128, b=2, s=40)
+    args = pdec.build_args(q, cache, torch.empty_like(q), sm_count=148)
+    for batch, expect in ((2048, 2), (2049, 1)):
+        args.batch = batch
+        assert lib.pd_select_kernel(ctypes.byref(args)) == expect, batch
+
+
 def test_simple_kernel_workspace_grows_with_splits():
     lib = _cabi.load()
     q, cache = _cpu_case(b=2, s=4096)

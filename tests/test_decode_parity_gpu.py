@@ -305,6 +305,27 @@ def test_many_requests_on_8bit_pages_with_eight_kv_heads(d, kv, scaled):
         helpers.assert_close(_run(case, "stream", splits), ref, what=f"many requests D{d} {kv}")
 
 
+@pytest.mark.parametrize("batch,kv_dtype", [(4096, "fp16"), (4097, "fp16"), (4096, "int8")])
+def test_batches_at_the_virtual_sequence_limit(batch, kv_dtype):
+    """4096 short requests are the most the streaming kernel lays out; one more and the automatic
+    choice is the general kernel.  Either way the oracle's result."""
+    rng = np.random.Generator(np.random.PCG64(batch))
+    lens = tuple(int(n) for n in rng.integers(0, 40, size=batch))
+    case = cases.Case(f"limit{batch}", 32, 8, 128, 16, kv_dtype, lens, seed=91)
+    q_np, oc = cases.build(case)
+    ref = c_oracle.decode(cases.q_as_f32(case, q_np), oc)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    args = pdec.build_args(q, cache, torch.empty_like(q))
+    assert pdec.selected_kernel(args) == ("stream" if batch <= 4096 else "simple")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):  # twice: 32 768 arrival counters must be left clean
+        out = pda.paged_decode(q, cache, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        helpers.assert_close(out, ref, what=f"{batch} requests, {kv_dtype}")
+
+
 @pytest.mark.parametrize("kv", ["int8", "fp8_e5m2"])
 def test_8bit_pages_with_32_byte_rows_take_the_general_kernel(kv):
     """head_dim 32 on 8-bit pages is a 32-byte row, which the streaming kernel does not serve:
