@@ -359,11 +359,12 @@ def e2e_steps(env: Env, cache, q, kernel: str, steps: int, job_bytes: float) -> 
     e2e_step = env.reduce([time.perf_counter() - t0], "max")[0] / steps
     return {"value": job_bytes / e2e_step / 1e9, "unit": "GB/s", "us_per_call": e2e_step * 1e6,
             "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes,
-            "note": "pd_decode_host, every step: q and lengths copied from pinned host memory; block-table entries "
-                    f"{'read by the kernel from the pinned host table (PD_FLAG_HOST_DIRECT_BT)' if 'bt' in env.args.e2e_direct else 'copied likewise'}; "
-                    f"result rows {'written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT)' if env.args.e2e_direct != 'none' and env.args.e2e_direct != 'q' else 'copied back'}; "
+            "note": "pd_decode_host, every step: lengths copied from pinned host memory; query rows "
+                    f"{'read by the kernel from the pinned host buffer (PD_FLAG_HOST_DIRECT_Q)' if 'q' in host.direct.split('+') or host.direct == 'both' else 'copied likewise'}; block-table entries "
+                    f"{'read by the kernel from the pinned host table (PD_FLAG_HOST_DIRECT_BT)' if 'bt' in host.direct else 'copied likewise'}; "
+                    f"result rows {'written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT)' if 'out' in host.direct or host.direct == 'both' else 'copied back'}; "
                     "h2d/d2h bytes count the buffers' full sizes; the KV pages are device state and stay in HBM",
-            "direct": env.args.e2e_direct}
+            "direct": host.direct}
 
 
 def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:
@@ -624,7 +625,7 @@ def main() -> None:
                          "(fused), a push kernel does (peer), or NCCL all-gather + merge (nccl)")
     ap.add_argument("--equal-tile-shares", action="store_true",
                     help="streaming kernel: equal tile counts per worker instead of equal estimated times (A/B)")
-    ap.add_argument("--e2e-direct", choices=("out+bt", "out", "none", "q", "both", "out+bt+q"), default="out+bt",
+    ap.add_argument("--e2e-direct", choices=("auto", "out+bt", "out", "none", "q", "both", "out+bt+q"), default="auto",
                     help="e2e: which pinned host buffers the kernels use in place instead of a staging copy "
                          "(PD_FLAG_HOST_DIRECT_OUT / _BT / _Q); none = every buffer staged (A/B)")
     ap.add_argument("--no-graph", action="store_true",

@@ -84,9 +84,19 @@ extern "C" {
                                       need (one 128-byte read per 32 tiles of a worker) across the bus
                                       instead of the whole padded table being copied ahead of them */
 #define PD_FLAG_HOST_DIRECT_Q 8u   /* the same for q_host: the kernels read the query rows from host
-                                      memory.  Pays only for small batches: a worker waits for its
-                                      query rows when a request starts, and across the bus that wait is
-                                      several times longer. */
+                                      memory (implies PD_FLAG_STAGE_Q).  A worker waits for its query
+                                      rows when a request starts, and across the bus that wait is
+                                      longer: it pays for batches of many requests (the copy it saves
+                                      grows with the batch) and costs a few microseconds where a few
+                                      long requests are cut over all workers, which then all fetch the
+                                      same rows at once. */
+#define PD_FLAG_STAGE_Q 32u        /* streaming kernel: a consumer warp first copies the query rows of
+                                      its kv head's group into shared memory with 16-byte loads (whole
+                                      128-byte lines) and takes its fragments from there, instead of
+                                      sixteen 4-byte loads per lane.  Needs the group's rows to be one
+                                      dense 16-byte-aligned run and room in shared memory, else it is
+                                      ignored.  No faster for q in device memory (0.2 us slower on
+                                      cache-resident batches), hence off unless asked for. */
 
 /* bits of the optional device status word (PdDecodeArgs.status) */
 #define PD_DEV_BAD_BLOCK 1u   /* a block-table entry was outside [0, num_blocks): page skipped */

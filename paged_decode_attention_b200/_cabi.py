@@ -105,6 +105,7 @@ FLAG_EQUAL_TILE_SHARES = 2
 FLAG_HOST_DIRECT_OUT = 4
 FLAG_HOST_DIRECT_Q = 8
 FLAG_HOST_DIRECT_BT = 16
+FLAG_STAGE_Q = 32
 EXCHANGE_SEND, EXCHANGE_MERGE = 1, 2
 
 STATIC_SCRATCH_BYTES = 8 << 20

@@ -334,6 +334,7 @@ int pd_decode_host(const PdDecodeArgs* args, const PdHostIO* io) {
     void* dq = device_view_of_host(io->q_host);
     if (dq && ((uintptr_t)dq % 16) == 0) {
       a.q = dq;
+      a.flags |= PD_FLAG_STAGE_Q;  // whole lines across the bus, not 4-byte pieces
       q_direct = true;
     }
   }

@@ -36,6 +36,7 @@ static int head_block(int hkv) {
 
 struct Shape {
   int hb, nhb, wpc, splits, nvseq, stage_bytes, seg_cost;
+  uint32_t qwarp_bytes;  // query staging one consumer warp would need; 0: the group's rows are not one dense run
   bool scaled;
 };
 
@@ -65,12 +66,17 @@ static Shape derive(const PdDecodeArgs* a) {
   // batches (0, 2, 4, 8, 12), the launches were shortest at 8 (ragged fp16: -1.2 %; uniform fp16:
   // -0.6 % from 4 upwards) and at 12 (int8: -1.0 %) - an end also delays the worker's producer.
   s.seg_cost = (a->flags & PD_FLAG_EQUAL_TILE_SHARES) ? 0 : (eb == 2 ? 8 : 12);
+  // on request (PD_FLAG_STAGE_Q) the kernel stages a group's query rows with 16-byte loads, when
+  // they are one aligned dense run
+  const bool q_dense = (a->flags & PD_FLAG_STAGE_Q) && a->q_stride_h == a->head_dim && ((uintptr_t)a->q % 16) == 0 &&
+                       (a->q_stride_b * 2) % 16 == 0;
+  s.qwarp_bytes = q_dense ? (uint32_t)(a->num_q_heads / a->num_kv_heads) * (uint32_t)(a->head_dim * 2 + 16) : 0u;
   return s;
 }
 
 struct SmemPlan {
   int nstage;
-  uint32_t bar_off, meta_off, misc_off, prefix_off, count_off, bound_off, total;
+  uint32_t bar_off, meta_off, misc_off, prefix_off, count_off, bound_off, qstage_off, qstage_warp_bytes, total;
 };
 
 static bool plan_smem(const Shape& s, SmemPlan& sm) {
@@ -92,6 +98,14 @@ static bool plan_smem(const Shape& s, SmemPlan& sm) {
   sm.count_off = sm.prefix_off + (uint32_t)(s.nvseq + 2) * 4;
   sm.bound_off = (sm.count_off + (uint32_t)(s.nvseq + 2) * 2 + 15u) & ~15u;
   sm.total = sm.bound_off + (uint32_t)(kMaxWorkers + 2) * 4 + 1024;
+  // query staging only where it costs no stage of the ring
+  sm.qstage_off = (sm.bound_off + (uint32_t)(kMaxWorkers + 2) * 4 + 15u) & ~15u;
+  sm.qstage_warp_bytes = 0;
+  const uint32_t qbytes = (uint32_t)(s.wpc * s.hb) * s.qwarp_bytes;
+  if (qbytes && (uint64_t)sm.qstage_off + qbytes + 1024 <= (uint64_t)kSmemLimit) {
+    sm.qstage_warp_bytes = s.qwarp_bytes;
+    sm.total = sm.qstage_off + qbytes + 1024;
+  }
   return true;
 }
 
@@ -253,6 +267,8 @@ static int launch_stream(const PdDecodeArgs* a, const Params& p, const Shape& s,
   sp.prefix_off = sm.prefix_off;
   sp.count_off = sm.count_off;
   sp.bound_off = sm.bound_off;
+  sp.qstage_off = sm.qstage_off;
+  sp.qstage_warp_bytes = sm.qstage_warp_bytes;
   sp.seg_cost = s.seg_cost;
   sp.tickets = (int32_t*)(scratch + wl.ticket_off);
   sp.scale_tx_bytes = (uint32_t)(kTileTokens * a->num_kv_heads * 2);

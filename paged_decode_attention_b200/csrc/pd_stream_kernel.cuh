@@ -86,6 +86,10 @@ struct StreamParams {
   Params p;
   int32_t nvseq, nhb, splits, nstage, wpc;
   uint32_t bar_off, meta_off, misc_off, prefix_off, count_off, bound_off;
+  // Query staging: qstage_warp_bytes > 0 when the query rows of one kv head's group are one dense
+  // run in q and shared memory has room; every consumer warp then owns that many bytes at
+  // qstage_off, rows at a pitch of head_dim * 2 + 16 bytes (the 16 spread the rows over the banks).
+  uint32_t qstage_off, qstage_warp_bytes;
   int32_t seg_cost;  // tiles' worth of time that one segment end costs a worker (0: shares of equal tile counts)
   int32_t* tickets;  // one arrival counter per (request, kv head), zero when the kernel starts
   uint32_t scale_tx_bytes;  // bytes of one scale copy: 16 tokens * Hkv * 2
@@ -199,6 +203,10 @@ __device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void lds64(uint32_t addr, uint32_t (&r)[2]) {
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
@@ -1082,30 +1090,56 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
     // ---- query rows of this kv head's group as B fragments: thread (g, t) holds head g (+8 per
     // n-tile), head_dim pairs of its k slots; heads >= group are zero --------------------------
     uint32_t qb[C::KSTEPS][NG][2];
+    // Where the group's rows are one dense run, the warp first copies them into its own piece of
+    // shared memory with 16-byte loads (a few full lines instead of sixteen 4-byte loads per lane
+    // that each touch eight rows: what makes reading q from pinned host memory affordable, one
+    // 128-byte read across the bus per line) and takes the fragments from there.
+    constexpr uint32_t kQPitch = D * 2 + 16;
+    const uint32_t qstage = sp.qstage_warp_bytes
+                                ? base + sp.qstage_off + (uint32_t)(wl * HB + role) * sp.qstage_warp_bytes
+                                : 0u;
+    if (qstage) {
+      constexpr int kRowChunks = D * 2 / 16;
+      const uint4* src = reinterpret_cast<const uint4*>((const __half*)p.q + (int64_t)vi.b * p.q_sb +
+                                                        (int64_t)kvh * p.group * p.q_sh);
+      __syncwarp();  // the fragment reads of the segment before are over
+      for (int i = lane; i < p.group * kRowChunks; i += 32)
+        sts128(qstage + (uint32_t)(i / kRowChunks) * kQPitch + (uint32_t)(i % kRowChunks) * 16u, __ldg(src + i));
+      __syncwarp();
+    }
+    // the two fetches are kept in two separate unrolled loops: one branch, not one per fragment
+    auto fill_fragments = [&](auto&& fetch) {
 #pragma unroll
-    for (int ng = 0; ng < NG; ++ng) {
-      const int head = 8 * ng + gq;
-      const bool live = head < p.group;
-      const __half* qrow = (const __half*)p.q + (int64_t)vi.b * p.q_sb +
-                           (int64_t)(kvh * p.group + (live ? head : 0)) * p.q_sh;
+      for (int ng = 0; ng < NG; ++ng) {
+        const int head = 8 * ng + gq;
+        const bool live = head < p.group;
 #pragma unroll
-      for (int ks = 0; ks < C::KSTEPS; ++ks) {
-        int c_lo, c_hi;  // head_dim index of k slots (2t, 2t+1) and (2t+8, 2t+9)
-        if constexpr (is_16bit(KV)) {
-          c_lo = 16 * ks + 2 * tq;
-          c_hi = c_lo + 8;
-        } else {
-          // every piece of an 8-bit row is read as its 16-byte chunks CPT*t .. CPT*t + CPT-1
-          // (CPT = 2 for 128-byte pieces, 1 for 64-byte rows); k-step ks uses word ks % 4 of the
-          // (ks / 4)-th chunk the thread reads, whose four elements fill its four k slots
-          constexpr int CPT = C::CPR / 4;
-          const int cj = ks >> 2;
-          c_lo = C::PITCH * (cj / CPT) + 16 * (CPT * tq + cj % CPT) + 4 * (ks & 3);
-          c_hi = c_lo + 2;
+        for (int ks = 0; ks < C::KSTEPS; ++ks) {
+          int c_lo, c_hi;  // head_dim index of k slots (2t, 2t+1) and (2t+8, 2t+9)
+          if constexpr (is_16bit(KV)) {
+            c_lo = 16 * ks + 2 * tq;
+            c_hi = c_lo + 8;
+          } else {
+            // every piece of an 8-bit row is read as its 16-byte chunks CPT*t .. CPT*t + CPT-1
+            // (CPT = 2 for 128-byte pieces, 1 for 64-byte rows); k-step ks uses word ks % 4 of the
+            // (ks / 4)-th chunk the thread reads, whose four elements fill its four k slots
+            constexpr int CPT = C::CPR / 4;
+            const int cj = ks >> 2;
+            c_lo = C::PITCH * (cj / CPT) + 16 * (CPT * tq + cj % CPT) + 4 * (ks & 3);
+            c_hi = c_lo + 2;
+          }
+          qb[ks][ng][0] = live ? fetch(head, c_lo) : 0u;
+          qb[ks][ng][1] = live ? fetch(head, c_hi) : 0u;
         }
-        qb[ks][ng][0] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_lo)) : 0u;
-        qb[ks][ng][1] = live ? __ldg(reinterpret_cast<const uint32_t*>(qrow + c_hi)) : 0u;
       }
+    };
+    if (qstage) {
+      fill_fragments([&](int head, int col) { return lds32(qstage + (uint32_t)head * kQPitch + 2u * (uint32_t)col); });
+    } else {
+      const __half* qrows = (const __half*)p.q + (int64_t)vi.b * p.q_sb + (int64_t)kvh * p.group * p.q_sh;
+      fill_fragments([&](int head, int col) {
+        return __ldg(reinterpret_cast<const uint32_t*>(qrows + (int64_t)head * p.q_sh + col));
+      });
     }
     // int8 keys meet the query on the integer tensor-core path.  Each query row is written as
     // step * (128 * hi + lo) with int8 digits hi in [-127, 127] and lo in [-64, 63], step =

@@ -409,14 +409,16 @@ class HostDecoder:
     ``"out"`` (result rows are written across the bus as they are finished, while the KV pages
     still stream: 3 to 13 % off a step of the five bench workloads), ``"bt"`` (the producers
     fetch the block-table entries they need across the bus instead of the whole padded table
-    being copied first: up to 5 % more), ``"q"`` (the query rows read across the bus too: pays
-    only for small batches such as the 24-request c1, a worker waits for them at every request
-    start; ``"both"`` = ``"out+q"``) or ``"none"``.  Default ``"out+bt"``.  Pageable host
-    tensors are always staged.
+    being copied first: up to 5 % more), ``"q"`` (every consumer warp fetches its group's query
+    rows across the bus, whole lines into shared memory, when a request starts: 5 to 35 % more
+    on batches of many requests, a few per cent worse where a few long requests are cut over all
+    workers, which then all want the same rows at once; ``"both"`` = ``"out+q"``) or
+    ``"none"``.  Default ``"auto"``: ``"out+bt"``, and ``"q"`` as well from 16 requests upwards.
+    Pageable host tensors are always staged.
     """
 
     def __init__(self, cache: PagedKVCache, io_dtype: torch.dtype = torch.float16,
-                 sm_scale: float | None = None, kernel: str = "auto", direct: str = "out+bt"):
+                 sm_scale: float | None = None, kernel: str = "auto", direct: str = "auto"):
         dev = cache.k_cache.device
         b, hq, d = cache.batch, cache.shape.num_q_heads, cache.shape.head_dim
         self.q_dev = torch.empty((b, hq, d), dtype=io_dtype, device=dev)
@@ -427,6 +429,9 @@ class HostDecoder:
         # staging buffers q_dev / out_dev (PD_FLAG_HOST_DIRECT_OUT, PD_FLAG_HOST_DIRECT_Q)
         bits = {"out": _cabi.FLAG_HOST_DIRECT_OUT, "q": _cabi.FLAG_HOST_DIRECT_Q, "bt": _cabi.FLAG_HOST_DIRECT_BT,
                 "none": 0, "both": _cabi.FLAG_HOST_DIRECT_OUT | _cabi.FLAG_HOST_DIRECT_Q}
+        if direct == "auto":
+            direct = "out+bt+q" if b >= 16 else "out+bt"
+        self.direct = direct
         for part in direct.split("+"):
             self.args.flags |= bits[part]
         need = ctypes.c_uint64(0)

@@ -51,11 +51,11 @@ def test_flag_and_size_constants_match_the_header():
         return eval(defines[name].replace("u", ""))  # noqa: S307 - literals of the header
 
     assert value("PD_ABI_VERSION") == _cabi.ABI_VERSION
-    for name in ("COUNTERS_ZERO", "EQUAL_TILE_SHARES", "HOST_DIRECT_OUT", "HOST_DIRECT_Q", "HOST_DIRECT_BT"):
+    for name in ("COUNTERS_ZERO", "EQUAL_TILE_SHARES", "HOST_DIRECT_OUT", "HOST_DIRECT_Q", "HOST_DIRECT_BT", "STAGE_Q"):
         assert value(f"PD_FLAG_{name}") == getattr(_cabi, f"FLAG_{name}"), name
     flags = [value(f"PD_FLAG_{n}") for n in ("COUNTERS_ZERO", "EQUAL_TILE_SHARES", "HOST_DIRECT_OUT", "HOST_DIRECT_Q",
-                                             "HOST_DIRECT_BT")]
-    assert sorted(flags) == [1, 2, 4, 8, 16]
+                                             "HOST_DIRECT_BT", "STAGE_Q")]
+    assert sorted(flags) == [1, 2, 4, 8, 16, 32]
     assert value("PD_STATIC_SCRATCH_BYTES") == _cabi.STATIC_SCRATCH_BYTES
     assert (value("PD_EXCHANGE_SEND"), value("PD_EXCHANGE_MERGE")) == (_cabi.EXCHANGE_SEND, _cabi.EXCHANGE_MERGE)
     assert (value("PD_DEV_BAD_BLOCK"), value("PD_DEV_TIMEOUT")) == (_cabi.DEV_BAD_BLOCK, _cabi.DEV_TIMEOUT)

@@ -391,6 +391,32 @@ def test_host_buffers_used_in_place_give_the_staged_result(name, direct):
     assert torch.equal(run(direct, pinned=False), staged), "pageable buffers are staged as before"
 
 
+@pytest.mark.parametrize("seed", range(0, 36, 3))
+def test_query_rows_staged_through_shared_memory_give_the_same_bits(seed):
+    """PD_FLAG_STAGE_Q: the consumer warps copy their group's query rows into shared memory with
+    16-byte loads and take the fragments from there.  The same values reach the same registers,
+    so the result is bit for bit that of the plain call - over head counts, groups (one and two
+    n-tiles), head_dim 64-256 and every page type; rows that are not one dense run ignore the flag."""
+    case, splits = _random_case(seed)
+    if sum(case.lens) == 0:
+        pytest.skip("degenerate draw")
+    q_np, oc = cases.build(case)
+    cache = helpers.to_device_cache(oc)
+    q = helpers.q_to_device(case, q_np)
+    probe = pdec.build_args(q, cache, torch.empty_like(q), num_splits=splits)
+    if pdec.selected_kernel(probe) != "stream":
+        pytest.skip("streaming kernel does not serve this shape")
+    plain = pda.DecodeStep(q, cache, num_splits=splits, kernel="stream").step().clone()
+    staged = pda.DecodeStep(q, cache, num_splits=splits, kernel="stream")
+    staged.args.flags |= _cabi.FLAG_STAGE_Q
+    assert torch.equal(staged.step(), plain)
+    wide = torch.zeros((q.shape[0], q.shape[1], q.shape[2] + 8), dtype=q.dtype, device="cuda")
+    wide[..., :q.shape[2]] = q
+    strided = pda.DecodeStep(wide[..., :q.shape[2]], cache, num_splits=splits, kernel="stream")
+    strided.args.flags |= _cabi.FLAG_STAGE_Q
+    assert torch.equal(strided.step(), plain)
+
+
 def test_rejects_bad_arguments_without_launching():
     case = cases.BY_NAME["llama8b_b2_s64"]
     q_np, oc = cases.build(case)
