@@ -336,35 +336,51 @@ def timed_steps(env: Env, step, steps: int, warmup: int, graph_steps: int = 0, c
 
 
 def e2e_steps(env: Env, cache, q, kernel: str, steps: int, job_bytes: float) -> dict:
-    """The same call through pd_decode_host: inputs from pinned host memory, result copied back."""
+    """The same call through pd_decode_host: inputs in pinned host memory, result into pinned host memory.
+
+    Timed twice: the way `--e2e-direct` names (default: the kernels use the caller's buffers in
+    place where that pays) and, for comparison, with every buffer staged through a device copy
+    by cudaMemcpyAsync ahead of and behind the kernel."""
     import paged_decode_attention_b200 as pda
 
     torch = env.torch
-    host = pda.HostDecoder(cache, kernel=kernel, direct=env.args.e2e_direct)
     q_h = q.cpu().pin_memory()
     bt_h = cache.block_table.cpu().pin_memory()
     sl_h = cache.seq_lens.cpu().pin_memory()
     out_h = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-    # Warm-up by time as well as by count: pinning the host copies above leaves the GPU idle for
-    # milliseconds, and the first steps after that run while its clocks are still coming back up.
-    warm_until, n = time.perf_counter() + 0.05, 0
-    while n < max(3, env.args.warmup) or time.perf_counter() < warm_until:
-        host.step(q_h, bt_h, sl_h, out_h)
-        n += 1
-    env.sync_all()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        host.step(q_h, bt_h, sl_h, out_h)
-    torch.cuda.synchronize()
-    e2e_step = env.reduce([time.perf_counter() - t0], "max")[0] / steps
-    return {"value": job_bytes / e2e_step / 1e9, "unit": "GB/s", "us_per_call": e2e_step * 1e6,
-            "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes,
-            "note": "pd_decode_host, every step: lengths copied from pinned host memory; query rows "
-                    f"{'read by the kernel from the pinned host buffer (PD_FLAG_HOST_DIRECT_Q)' if 'q' in host.direct.split('+') or host.direct == 'both' else 'copied likewise'}; block-table entries "
-                    f"{'read by the kernel from the pinned host table (PD_FLAG_HOST_DIRECT_BT)' if 'bt' in host.direct else 'copied likewise'}; "
-                    f"result rows {'written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT)' if 'out' in host.direct or host.direct == 'both' else 'copied back'}; "
-                    "h2d/d2h bytes count the buffers' full sizes; the KV pages are device state and stay in HBM",
-            "direct": host.direct}
+
+    def timed(host) -> float:
+        # Warm-up by time as well as by count: pinning the host copies above leaves the GPU idle
+        # for milliseconds, and the first steps after that run while its clocks are still coming
+        # back up.
+        warm_until, n = time.perf_counter() + 0.05, 0
+        while n < max(3, env.args.warmup) or time.perf_counter() < warm_until:
+            host.step(q_h, bt_h, sl_h, out_h)
+            n += 1
+        env.sync_all()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            host.step(q_h, bt_h, sl_h, out_h)
+        torch.cuda.synchronize()
+        return env.reduce([time.perf_counter() - t0], "max")[0] / steps
+
+    host = pda.HostDecoder(cache, kernel=kernel, direct=env.args.e2e_direct)
+    e2e_step = timed(host)
+    parts = host.direct.replace("both", "out+q").split("+")
+    res = {"value": job_bytes / e2e_step / 1e9, "unit": "GB/s", "us_per_call": e2e_step * 1e6,
+           "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes,
+           "note": "pd_decode_host, every step: lengths copied from pinned host memory; query rows "
+                   f"{'read by the kernel from the pinned host buffer (PD_FLAG_HOST_DIRECT_Q)' if 'q' in parts else 'copied likewise'}; block-table entries "
+                   f"{'read by the kernel from the pinned host table (PD_FLAG_HOST_DIRECT_BT)' if 'bt' in parts else 'copied likewise'}; "
+                   f"result rows {'written by the kernel into the pinned host buffer (PD_FLAG_HOST_DIRECT_OUT)' if 'out' in parts else 'copied back'}; "
+                   "h2d/d2h bytes count the buffers' full sizes; the KV pages are device state and stay in HBM",
+           "direct": host.direct}
+    if parts != ["none"]:
+        staged = timed(pda.HostDecoder(cache, kernel=kernel, direct="none"))
+        res["all_buffers_staged"] = {"us_per_call": staged * 1e6, "value": job_bytes / staged / 1e9, "unit": "GB/s",
+                                     "note": "the same steps with q, block table and lengths copied in and the result "
+                                             "copied back by cudaMemcpyAsync around the kernel"}
+    return res
 
 
 def measure_request_sharded(env: Env, name: str, strong: bool) -> dict:
