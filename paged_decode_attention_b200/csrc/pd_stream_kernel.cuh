@@ -932,11 +932,16 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
   // end when the cut falls into the surcharge.  A cut advances by more than seg_cost + 1, so no
   // cell between two others is empty.  Everything is a function of the lengths: all CTAs
   // derive the same boundaries, and two launches over the same lengths the same ones.
+  // A small batch of short requests (fewer virtual sequences than workers, none longer than
+  // kWholeTiles tiles) is dealt out whole, one request per worker, spread over the CTAs first:
+  // every output row is then written directly, with no partial, ticket or merge on the way, and
+  // nobody needs the boundaries (a call this short feels the barrier they would cost).
+  const bool dealt_whole = sp.splits == 1 && nv <= workers && *longest <= kWholeTiles && !pushing;
   const int sc = sp.seg_cost;
   const long long total_c = (long long)total + (long long)sc * nonempty[nv];
   long long per_c = (total_c + workers - 1) / workers;
   if (per_c < kMinTilesPerWorker + sc) per_c = kMinTilesPerWorker + sc;
-  for (int i = tid; i <= workers; i += kThreads) {
+  for (int i = tid; i <= workers && !dealt_whole; i += kThreads) {
     const long long c = (long long)i * per_c;
     int tile = total;
     if (c < total_c) {
@@ -952,18 +957,18 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
     }
     bound[i] = tile;
   }
-  __syncthreads();
+  if (!dealt_whole) __syncthreads();  // the same for the whole CTA: it is derived from shared values
   CellMap cm;
   cm.bound = bound;
   cm.workers = workers;
-  int g0 = bound[w], g1 = bound[w + 1];
-  // A small batch of short requests (fewer virtual sequences than workers, none longer than
-  // kWholeTiles tiles) is dealt out whole, one request per worker, spread over the CTAs first:
-  // every output row is then written directly, with no partial, ticket or merge on the way.
-  if (sp.splits == 1 && nv <= workers && *longest <= kWholeTiles && !pushing) {
+  int g0, g1;
+  if (dealt_whole) {
     const int mine = wl * gridDim.x + blockIdx.x;
     g0 = mine < nv ? prefix[mine] : total;
     g1 = mine < nv ? prefix[mine + 1] : total;
+  } else {
+    g0 = bound[w];
+    g1 = bound[w + 1];
   }
   if (blockIdx.x == 0) {
     // requests without a single token are nobody's work: their rows are zero, their lse -inf
