@@ -1220,8 +1220,10 @@ stream_decode_kernel(const __grid_constant__ StreamParams sp, const __grid_const
 
     // 8-bit tiles with a deep ring (five stages or more) are taken two at a time: one softmax
     // step per 32 tokens and two independent score chains per warp.  With fewer stages the
-    // second stage held by the consumers would cost the producer its lead.
-    constexpr bool kPairs = !is_16bit(KV);
+    // second stage held by the consumers would cost the producer its lead.  16-bit rows of up to
+    // 128 bytes (head_dim 64 and below: small stages, a deep ring) do the same: their requests
+    // are short and a warp's chain of softmax steps is most of such a call.
+    constexpr bool kPairs = !is_16bit(KV) || D <= 64;
     const bool pairs = kPairs && nstage >= 5;
     while (g < seg_end) {
       const int st = it % nstage;
